@@ -111,9 +111,14 @@ class PageGroup:
 
 class CacheManager:
     def __init__(self, state_specs: Sequence[object], num_pages: int, num_slots: int,
-                 cache_dtype: torch.dtype = torch.float32, device=None):
-        """``state_specs[i]`` is what schedule position i keeps: ``PagedKV``, ``FixedState``
-        or ``None``.  ``num_pages`` pages per group, ``num_slots`` live requests at most."""
+                 cache_dtype: torch.dtype = torch.float32, device=None,
+                 shares: Optional[Sequence[Optional[int]]] = None):
+        """``state_specs[i]`` is what schedule position i keeps: ``PagedKV``, ``FixedState``,
+        ``None``, or a tuple of one ``PagedKV`` and one ``FixedState`` (entries past the schedule
+        belong to the model itself: its embedding's state).  ``shares[i]`` names an earlier
+        position whose pages position i reads: its ``LayerCache`` gets that position's pools and
+        group beside whatever fixed state is its own.  ``num_pages`` pages per group,
+        ``num_slots`` live requests at most."""
         self.num_pages = int(num_pages)
         self.num_slots = int(num_slots)
         self.device = device
@@ -128,23 +133,38 @@ class CacheManager:
         self._admissions = 0
         self.slots_high_water = 0
         by_window: Dict[int, int] = {}
+        self._fixed_specs: Dict[int, FixedState] = {}
         for position, spec in enumerate(state_specs):
+            members = spec if isinstance(spec, tuple) else (() if spec is None else (spec,))
+            paged = [m for m in members if isinstance(m, PagedKV)]
+            fixed = [m for m in members if isinstance(m, FixedState)]
+            if len(paged) + len(fixed) != len(members) or len(paged) > 1 or len(fixed) > 1:
+                raise TypeError(f"schedule position {position}: unknown state spec {spec!r} (one PagedKV "
+                                "and one FixedState at most)")
             cache = LayerCache(spec=spec)
-            if isinstance(spec, PagedKV):
-                if spec.window not in by_window:
-                    by_window[spec.window] = len(self.groups)
-                    self.groups.append(PageGroup(spec.window, PagePool(self.num_pages)))
-                cache.group = by_window[spec.window]
+            if paged:
+                kv = paged[0]
+                if kv.window not in by_window:
+                    by_window[kv.window] = len(self.groups)
+                    self.groups.append(PageGroup(kv.window, PagePool(self.num_pages)))
+                cache.group = by_window[kv.window]
                 self.groups[cache.group].members.append(position)
                 if device is not None:
-                    shape = (self.num_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
+                    shape = (self.num_pages, kv.n_kv_heads, PAGE_SIZE, kv.head_dim)
                     cache.k_pool = torch.zeros(shape, dtype=cache_dtype, device=device)
-                    cache.v_pool = torch.zeros(shape, dtype=cache_dtype, device=device)
-            elif isinstance(spec, FixedState):
+                    if kv.values:
+                        cache.v_pool = torch.zeros(shape, dtype=cache_dtype, device=device)
+            if fixed:
                 self._fixed_positions.append(position)
-            elif spec is not None:
-                raise TypeError(f"schedule position {position}: unknown state spec {spec!r}")
+                self._fixed_specs[position] = fixed[0]
             self.layer_caches.append(cache)
+        for position, source in enumerate(shares or ()):
+            if source is None:
+                continue
+            cache, origin = self.layer_caches[position], self.layer_caches[source]
+            if not 0 <= source < position or cache.group is not None:
+                raise ValueError(f"schedule position {position} cannot read the pages of position {source}")
+            cache.group, cache.k_pool, cache.v_pool = origin.group, origin.k_pool, origin.v_pool
         self._windowed = any(group.window for group in self.groups)
         self._rows: List[Dict[Hashable, tuple]] = [{} for _ in self.groups]   # block-table rows as arrays
         # All fixed-size states of one dtype lie side by side in one allocation, [num_slots][total],
@@ -153,7 +173,7 @@ class CacheManager:
         if device is not None and self._fixed_positions:
             by_dtype: Dict[torch.dtype, List[Tuple[int, int]]] = {}
             for position in self._fixed_positions:
-                spec = self.layer_caches[position].spec
+                spec = self._fixed_specs[position]
                 count = 1
                 for extent in spec.shape:
                     count *= int(extent)
@@ -164,7 +184,7 @@ class CacheManager:
                 self._all_states[dtype] = pool
                 offset = 0
                 for position, count in members:
-                    shape = tuple(self.layer_caches[position].spec.shape)
+                    shape = tuple(self._fixed_specs[position].shape)
                     self.layer_caches[position].state = (
                         pool[:, offset:offset + count].unflatten(1, shape) if shape else pool[:, offset])
                     offset += count

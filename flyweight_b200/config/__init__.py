@@ -1,10 +1,11 @@
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .lfm2 import ConfigError, Lfm2Config
+from .kemitar import KemitarConfig
 from .registry import (Architecture, UnknownArchitecture, architecture_name, architectures,
                        load_config, lookup, read_config_json, register_architecture)
 
 __all__ = [
-    "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "ConfigError", "Lfm2Config",
+    "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "ConfigError", "Lfm2Config", "KemitarConfig",
     "Architecture", "UnknownArchitecture", "architecture_name", "architectures", "load_config",
     "lookup", "read_config_json", "register_architecture",
 ]

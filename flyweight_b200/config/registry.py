@@ -47,6 +47,8 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
     names = raw.get("architectures")
     if names:
         return str(names[0])
+    if raw.get("architecture"):                  # some configurations name the one architecture directly
+        return str(raw["architecture"])
     raise UnknownArchitecture("config.json has no 'architectures' entry; this engine runs: "
                               + ", ".join(architectures()))
 

@@ -66,8 +66,9 @@ class ScheduleEntry:
 
     ``layer`` indexes ``ModelSpec.layers``; a layer may appear in several entries
     (its weights are then shared, each execution keeping a cache of its own).
-    ``cache_of`` names an earlier schedule position whose cache this execution
-    reads instead of keeping one.
+    ``cache_of`` names an earlier schedule position whose keys (or latents) this
+    execution reads instead of keeping its own; per-request state of fixed size that the
+    layer's parts ask for stays its own.
     """
     layer: int
     cache_of: Optional[int] = None
@@ -85,6 +86,7 @@ class ModelSpec:
     layers: Tuple[LayerSpec, ...]
     schedule: Tuple[ScheduleEntry, ...]
     embedding_scale: float = 1.0        # embedding rows are multiplied by this (LFM2: 1)
+    embedding: Optional[PartSpec] = None  # None: the plain table lookup; else an embedding part
     logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap) (LFM2: off)
 
     def validate(self) -> None:

@@ -442,6 +442,8 @@ def build_plan(model, caches, max_tokens: int, max_rows: int, num_slots: int, n_
     builder = PlanBuilder(model.precision, model.device, spec.hidden_size, max_tokens, max_rows, num_slots,
                           bad_flag)
     try:
+        if getattr(model, "embedder", None) is not None:
+            raise NotPlannable(f"embedding {model.embedder.kind!r} has no native form")
         builder.embed(model.embedding, spec.vocab_size, spec.embedding_scale)
         for position, entry in enumerate(spec.schedule):
             source = position if entry.cache_of is None else entry.cache_of

@@ -188,7 +188,8 @@ class ModelRunner(StepPlanner):
                             f"{model.spec.max_positions} positions")
         model.prepare(int(max_model_len))
         cache = CacheManager(model.state_specs(), num_pages, num_slots,
-                             cache_dtype=self.precision.cache_dtype, device=self.device)
+                             cache_dtype=self.precision.cache_dtype, device=self.device,
+                             shares=model.cache_sources())
         super().__init__(cache, model.spec.vocab_size, max_model_len, max_batched_tokens)
         self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the forward pass of a step as one native call, when every part of the model has that form

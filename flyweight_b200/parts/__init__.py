@@ -1,12 +1,15 @@
-from .base import (Arrangement, FeedForward, FixedState, Mixer, Norm, PagedKV, Part,
-                   PositionEncoding, Precision, build_arrangement, build_feed_forward,
+from .base import (Arrangement, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part,
+                   PositionEncoding, Precision, StreamShift, build_arrangement, build_embedding,
+                   build_feed_forward, build_shift,
                    build_mixer, build_norm, build_position, register_arrangement,
-                   register_feed_forward, register_mixer, register_norm, register_position)
-from . import attention, block, norm, rope, shortconv, swiglu  # noqa: F401  (register the parts)
+                   register_embedding, register_feed_forward, register_mixer, register_norm,
+                   register_position, register_shift)
+from . import (attention, block, embedding, latent_attention, norm, outnorm_block, rope, shortconv,  # noqa: F401
+               swiglu, token_shift)  # noqa: F401  (register the parts)
 
 __all__ = [
-    "Arrangement", "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "Part",
-    "PositionEncoding", "Precision", "build_arrangement", "build_feed_forward", "build_mixer",
+    "Arrangement", "Embedding", "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "Part",
+    "PositionEncoding", "Precision", "StreamShift", "build_arrangement", "build_embedding", "build_shift", "build_feed_forward", "build_mixer",
     "build_norm", "build_position", "register_arrangement", "register_feed_forward",
-    "register_mixer", "register_norm", "register_position",
+    "register_mixer", "register_norm", "register_position", "register_embedding", "register_shift",
 ]

@@ -24,6 +24,11 @@ Interfaces
 ``PositionEncoding.encode(ctx, qkv, ...)`` -> q; keys and values are in the cache afterwards.
     The default is the fused norm + rotation + page-write kernel fed by ``table(n_positions,
     device)``, ``rotary_dim`` and ``pairing``.
+``Embedding.forward(ctx, table, cache)`` -> fp32 [T][H]
+    what enters the first layer; ``state_spec()`` as for a mixer (a ``FixedState`` or None).
+``StreamShift.forward(ctx, x, cache)`` -> rows in ``ctx.precision.act_dtype``
+    a mix of the residual stream along the sequence in front of a mixer (a token shift); it keeps
+    what it needs of a request's earlier tokens in a ``FixedState``.
 ``Arrangement.forward(ctx, x, pending, cache)`` -> (x, pending)
     wires norms, mixer and feed-forward around the residual stream; ``pending`` is
     a delta not yet added to x, handed to the next norm so that the sum and the
@@ -83,6 +88,7 @@ class PagedKV:
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True        # False: one pool only (a latent row per token serves as key and value)
 
 
 @dataclass(frozen=True)
@@ -227,6 +233,28 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """What enters the first layer for the step's tokens.  The model owns the token table (the head
+    may be tied to it) and hands it in; an embedding part adds what else it needs (``declare``,
+    ``bind``) and may keep per-request state of fixed size (``state_spec``)."""
+
+    def state_spec(self):
+        return None
+
+    def forward(self, ctx, table, cache):
+        raise NotImplementedError
+
+
+class StreamShift(Part):
+    """A mix of the fp32 residual stream along the sequence, in front of a mixer."""
+
+    def state_spec(self):
+        return None
+
+    def forward(self, ctx, x, cache):
+        raise NotImplementedError
+
+
 class Arrangement:
     """How a layer's parts are wired around the residual stream.  ``ROLES`` maps each role name
     the arrangement knows to the family its part is built from (``norm``, ``mixer``,
@@ -246,7 +274,8 @@ class Arrangement:
                              + (f"unknown parts {unknown}; " if unknown else "")
                              + (f"missing parts {missing}; " if missing else "")
                              + "it wires " + ", ".join(self.ROLES))
-        builders = {"norm": build_norm, "mixer": build_mixer, "feed_forward": build_feed_forward}
+        builders = {"norm": build_norm, "mixer": build_mixer, "feed_forward": build_feed_forward,
+                    "shift": build_shift}
         self._built = []
         for role, (family, _) in self.ROLES.items():
             part = builders[family](layer.parts[role]) if role in layer.parts else None
@@ -263,8 +292,20 @@ class Arrangement:
         return getattr(self, "mixer", None)
 
     def state_spec(self):
+        """What one execution of this layer keeps: None, one spec, or a tuple of specs (at most one
+        ``PagedKV`` and one ``FixedState``) when several of its parts keep something."""
+        specs = []
+        for part in self.stateful_parts():
+            spec = part.state_spec()
+            if spec is not None:
+                specs.extend(spec if isinstance(spec, tuple) else (spec,))
+        if not specs:
+            return None
+        return specs[0] if len(specs) == 1 else tuple(specs)
+
+    def stateful_parts(self):
         part = self.stateful_part()
-        return part.state_spec() if part is not None else None
+        return () if part is None else (part,)
 
     def prepare(self, max_positions: int, device) -> None:
         for part in self._built:
@@ -282,6 +323,8 @@ _MIXERS: Dict[str, type] = {}
 _FEED_FORWARDS: Dict[str, type] = {}
 _POSITIONS: Dict[str, type] = {}
 _ARRANGEMENTS: Dict[str, type] = {}
+_EMBEDDINGS: Dict[str, type] = {}
+_SHIFTS: Dict[str, type] = {}
 
 
 def _register(table: Dict[str, type], what: str):
@@ -299,6 +342,8 @@ register_mixer = _register(_MIXERS, "mixer")
 register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
 register_position = _register(_POSITIONS, "position encoding")
 register_arrangement = _register(_ARRANGEMENTS, "arrangement")
+register_embedding = _register(_EMBEDDINGS, "embedding")
+register_shift = _register(_SHIFTS, "stream shift")
 
 
 def _build(table: Dict[str, type], what: str, spec: PartSpec):
@@ -324,6 +369,14 @@ def build_feed_forward(spec: PartSpec) -> FeedForward:
 
 def build_position(spec: PartSpec) -> PositionEncoding:
     return _build(_POSITIONS, "position encoding", spec)
+
+
+def build_embedding(spec: PartSpec) -> Embedding:
+    return _build(_EMBEDDINGS, "embedding", spec)
+
+
+def build_shift(spec: PartSpec) -> StreamShift:
+    return _build(_SHIFTS, "stream shift", spec)
 
 
 def build_arrangement(layer: LayerSpec) -> Arrangement:

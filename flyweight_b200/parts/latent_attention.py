@@ -1,0 +1,132 @@
+"""Attention over a cached low-rank latent, with a softmax sink.
+
+Per token one projection gives ``rank + rot`` numbers: the first ``rank``, RMS-normed with a
+weight, are the latent c; the last ``rot``, turned by the token's position, are a key part r that
+every head shares.  Head h has the key ``(U_h c | r)`` and the value ``V_h c``; its query has
+``dim`` plain channels and ``rot`` turned ones; the score is ``scale * (q_plain . U_h c + q_rot . r)``
+and the causal softmax's denominator also holds ``exp(sink_h)``.  Only (c | r) is cached: one row per
+token for all heads, and a layer may read the rows another layer wrote (``shares_cache``) with
+projections U, V of its own.
+
+How it is computed: ``q_plain . U_h c = (U_h^T q_plain) . c``, so every query head is turned into a
+row ``(U_h^T q_plain | q_rot)`` of the cache row's layout, attention runs between many query heads
+and the one cached row per token, with the row's first ``rank`` columns as values, and V_h is
+applied to the weighted sum of latents afterwards.  Nothing per head is ever built for a cached
+token, whether the step is a whole prompt, a portion or one token.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import latent as latent_kernels
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import Mixer, PagedKV, Precision, build_position, register_mixer
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    """params: hidden_size, num_heads, dim (plain query/key channels per head), rot_dim (turned
+    ones), vdim, kv_rank, scale, eps (of the latent's norm), position (PartSpec of a rotary encoding
+    whose ``rotary_dim`` <= rot_dim), sink (True: a learned number per head joins the softmax
+    denominator), shares_cache (True: reads the rows of another execution; no latent projection).
+    tensors: q, dkv, dkv_norm, uk, uv, o, sink."""
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["num_heads"])
+        self.dim = int(p["dim"])
+        self.rot = int(p["rot_dim"])
+        self.vdim = int(p["vdim"])
+        self.rank = int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        self.has_sink = bool(p.get("sink", False))
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.position = build_position(p["position"])
+        if self.position.rotary_dim > self.rot:
+            raise ValueError(f"{self.position.rotary_dim} turning channels but a rotated part of {self.rot}")
+        if min(self.n_heads, self.dim, self.vdim, self.rank) <= 0 or self.rot < 0:
+            raise ValueError("latent attention: heads, dim, vdim and kv_rank must be positive")
+        # a cache row: latent, turned key part, zero padding up to a multiple of 16 entries
+        self.row = _round_up(self.rank + self.rot, 16)
+        self.q_width = self.n_heads * (self.dim + self.rot)
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = self.sink = None
+
+    def declare(self):
+        n, H = self.names, self.hidden
+        out = {n["q"]: TensorDecl((self.q_width, H)),
+               n["uk"]: TensorDecl((self.n_heads * self.dim, self.rank)),
+               n["uv"]: TensorDecl((self.n_heads * self.vdim, self.rank)),
+               n["o"]: TensorDecl((H, self.n_heads * self.vdim))}
+        if not self.shares_cache:
+            out[n["dkv"]] = TensorDecl((self.rank + self.rot, H))
+            out[n["dkv_norm"]] = TensorDecl((self.rank,), "norm")
+        if self.has_sink:
+            out[n["sink"]] = TensorDecl((self.n_heads,), "bias")
+        return out
+
+    def bind(self, get, precision: Precision, device):
+        n = self.names
+        mats = [get(n["q"])] + ([] if self.shares_cache else [get(n["dkv"])])
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.to(torch.float32) for m in mats]
+        # one projection for the queries and the latent: the rows of the two matrices, one after the other
+        self.w_in = precision.matrix(torch.cat(mats, dim=0), device)
+        # U as [heads][rank][dim]: the product that carries a plain query into the latent's space
+        uk = get(n["uk"]).reshape(self.n_heads, self.dim, self.rank).transpose(1, 2)
+        self.w_uk_t = precision.matrix(uk.contiguous(), device)
+        self.w_uv = precision.matrix(get(n["uv"]).reshape(self.n_heads, self.vdim, self.rank), device)
+        self.w_o = precision.matrix(get(n["o"]), device)
+        if not self.shares_cache:
+            self.norm_w = precision.vector(get(n["dkv_norm"]), device)
+        if self.has_sink:
+            self.sink = precision.vector(get(n["sink"]), device)
+
+    def _matrices(self):
+        return (self.w_in, self.w_uk_t, self.w_uv, self.w_o)
+
+    def weight_bytes(self):
+        return sum(m.numel() * m.element_size() for m in self._matrices())
+
+    def flops_per_token(self):
+        return 2.0 * sum(m.numel() for m in self._matrices())
+
+    def context_flops(self, n_tokens):
+        # scores over rank + rot columns, weighted sums over rank; half the pairs are masked
+        return 1.0 * n_tokens * n_tokens * self.n_heads * (2 * self.rank + self.rot)
+
+    def state_spec(self):
+        return None if self.shares_cache else PagedKV(1, self.row, 0, values=False)
+
+    def prepare(self, max_positions, device):
+        self.position.prepare(max_positions, device)
+
+    def forward(self, ctx, h, cache):
+        act = ctx.precision.act_dtype
+        batch = ctx.batch
+        rotation = self.position.rotation()
+        if rotation is None:
+            raise ValueError(f"latent attention turns its rotated part itself; position encoding "
+                             f"{self.position.kind!r} is no plain rotation")
+        table, rot_dims, pairing = rotation
+        block_table = batch.block_tables[cache.group]
+        proj = ops.linear(h, self.w_in, act)                     # [T][queries | latent + key part]
+        qa = latent_kernels.latent_prepare(
+            proj, self.q_width, self.norm_w, table, batch, block_table,
+            None if self.shares_cache else cache.k_pool, self.n_heads, self.dim, self.rot, rot_dims, pairing,
+            self.rank, self.row, self.eps)
+        qa2 = qa.view(qa.shape[0], self.n_heads * self.row)
+        latent_kernels.head_linear(proj, 0, self.dim + self.rot, self.dim, self.w_uk_t, qa2, 0, self.row)
+        mixed = latent_kernels.latent_attention(qa, cache.k_pool, self.sink, batch, block_table, self.rank,
+                                                self.rank + self.rot, self.scale)
+        heads_out = torch.empty((mixed.shape[0], self.n_heads * self.vdim), dtype=act, device=mixed.device)
+        latent_kernels.head_linear(mixed, 0, self.rank, self.rank, self.w_uv, heads_out, 0, self.vdim)
+        return ops.linear(heads_out, self.w_o, torch.float32)

@@ -16,7 +16,7 @@ import torch
 from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..weights.loader import TensorDecl, bind as bind_tensors
-from .base import Arrangement, Precision, build_arrangement, build_norm
+from .base import Arrangement, PagedKV, Precision, build_arrangement, build_embedding, build_norm
 
 
 class DecoderModel:
@@ -27,11 +27,16 @@ class DecoderModel:
         self.device = device
         self.layers: List[Arrangement] = [build_arrangement(layer) for layer in spec.layers]
         self.final_norm = build_norm(spec.final_norm)
+        # None: rows of the token table times ``embedding_scale``; else a part that builds the first
+        # layer's input from the table and whatever else it declares
+        self.embedder = build_embedding(spec.embedding) if spec.embedding is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         for position, entry in enumerate(spec.schedule):
             layer = self.layers[entry.layer]
-            if entry.cache_of is not None and layer.state_spec() is not None:
+            own = layer.state_spec()
+            own = own if isinstance(own, tuple) else (own,)
+            if entry.cache_of is not None and any(isinstance(s, PagedKV) for s in own):
                 raise ValueError(
                     f"schedule position {position} reads the cache of position {entry.cache_of}, "
                     f"but its mixer ({layer.stateful_part().kind}) keeps a cache of its own")
@@ -43,6 +48,8 @@ class DecoderModel:
         if spec.head_tensor is not None:
             out[spec.head_tensor] = TensorDecl((spec.vocab_size, spec.hidden_size))
         out.update(self.final_norm.declare())
+        if self.embedder is not None:
+            out.update(self.embedder.declare())
         for layer in self.layers:
             for part in layer.parts():
                 out.update(part.declare())
@@ -57,6 +64,8 @@ class DecoderModel:
         self.head = (self.embedding if spec.head_tensor is None
                      else precision.matrix(get(spec.head_tensor), device))
         self.final_norm.bind(get, precision, device)
+        if self.embedder is not None:
+            self.embedder.bind(get, precision, device)
         for layer in self.layers:
             for part in layer.parts():
                 part.bind(get, precision, device)
@@ -65,16 +74,24 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         """Every part only launches kernels over the step's device buffers."""
         return all(part.graph_safe for layer in self.layers for part in layer.parts()) \
-            and self.final_norm.graph_safe
+            and self.final_norm.graph_safe and (self.embedder is None or self.embedder.graph_safe)
 
     def prepare(self, max_positions: int) -> None:
         for layer in self.layers:
             layer.prepare(max_positions, self.device)
 
     def state_specs(self) -> list:
-        """What each schedule position keeps in the cache manager."""
-        return [None if entry.cache_of is not None else self.layers[entry.layer].state_spec()
-                for entry in self.spec.schedule]
+        """What each schedule position keeps in the cache manager (a position that reads another's
+        pages keeps only the fixed-size state of its own parts); one more entry, behind the
+        schedule, for the embedding part when it keeps something."""
+        specs = [self.layers[entry.layer].state_spec() for entry in self.spec.schedule]
+        if self.embedder is not None and self.embedder.state_spec() is not None:
+            specs.append(self.embedder.state_spec())
+        return specs
+
+    def cache_sources(self) -> list:
+        """For each schedule position the earlier position whose pages it reads, or None."""
+        return [entry.cache_of for entry in self.spec.schedule]
 
     def weight_bytes(self, with_embedding_rows: int = 0) -> int:
         """Bytes of weights one step reads: every scheduled layer once, the final norm, the
@@ -108,11 +125,16 @@ class DecoderModel:
         """Logits [R][V] fp32 at ``ctx.batch.logit_rows`` (an empty tensor if R == 0).
         ``caches[i]`` is the ``LayerCache`` of schedule position i."""
         batch = ctx.batch
-        x = ops.embed(self.embedding, batch.token_ids, ctx.bad_token_flag, self.spec.embedding_scale)
+        if self.embedder is None:
+            x = ops.embed(self.embedding, batch.token_ids, ctx.bad_token_flag, self.spec.embedding_scale)
+        else:
+            own = len(self.spec.schedule)
+            x = self.embedder.forward(ctx, self.embedding, caches[own] if len(caches) > own else None)
         pending = None
         for position, entry in enumerate(self.spec.schedule):
-            source = position if entry.cache_of is None else entry.cache_of
-            x, pending = self.layers[entry.layer].forward(ctx, x, pending, caches[source])
+            # a position that reads another's pages finds them in its own entry (the manager puts
+            # them there), beside the fixed-size state that is its own
+            x, pending = self.layers[entry.layer].forward(ctx, x, pending, caches[position])
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         n = self.final_norm.defer(ctx, x, rows=batch.logit_rows) if pending is None else None

@@ -41,3 +41,44 @@ class RMSNorm(Norm):
     def plan_params(self):
         """(weight, eps): what the native step plan needs to run this norm in front of a product."""
         return self.weight, self.eps
+
+
+@register_norm("rms_gain")
+class RMSGain(Norm):
+    """RMS norm with a single gain for all channels: ``g * x / sqrt(mean(x^2) + eps)``.
+    params: size, eps.  tensors: weight [] (one number).
+
+    In front of a product (``forward``, ``defer``) it is the ordinary RMS norm with the gain in every
+    channel.  Behind a sublayer (``add_normed``) it adds the normed rows into the residual stream."""
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(self.params["size"])
+        self.eps = float(self.params["eps"])
+        self.gain = self.weight = None
+
+    def declare(self):
+        return {self.names["weight"]: TensorDecl((), "norm", also=((1,),))}
+
+    def bind(self, get, precision: Precision, device):
+        self.gain = precision.vector(get(self.names["weight"]).reshape(1), device)
+        self.weight = self.gain.expand(self.size).contiguous()
+
+    def weight_bytes(self):
+        return 4
+
+    def forward(self, ctx, x, delta=None, rows=None):
+        return ops.rmsnorm(x, self.weight, self.eps, ctx.precision.act_dtype, delta=delta, rows=rows)
+
+    def defer(self, ctx, x, rows=None):
+        return DeferredNorm(x, self.weight, self.eps, rows)
+
+    def plan_params(self):
+        return self.weight, self.eps
+
+    def add_normed(self, ctx, x, y, copy_dtype=None):
+        """``x += g * y / sqrt(mean(y^2) + eps)`` in fp32, in place; with ``copy_dtype`` the new rows
+        are also returned in that dtype."""
+        from ..kernels import latent as latent_kernels
+        return latent_kernels.unit_rms_gain_add_(x, y, self.gain, self.eps, copy_dtype)
