@@ -113,11 +113,12 @@ def _open_runtime(args, context):
 
 def _generate(args) -> int:
     import random
-    from .config.registry import read_config_json
     if args.prompt:
         prompt = _ids(args.prompt)
     elif args.random_prompt:
-        vocab = int(read_config_json(args.model)["vocab_size"])
+        from . import models  # noqa: F401
+        from .config.registry import load_config
+        vocab = int(load_config(args.model)[1].model_spec().vocab_size)
         rng = random.Random(args.seed or 0)
         prompt = [rng.randrange(vocab) for _ in range(args.random_prompt)]
     else:

@@ -9,8 +9,16 @@ from pathlib import Path
 import numpy as np
 import torch
 
-import plain_lfm2 as P
-from tiny_configs import TINY, make_model_dir
+import plain_kemitar
+import plain_lfm2
+from tiny_configs import TINY, make_model_dir, vocab_of
+
+P = plain_lfm2
+
+
+def plain_module(name: str):
+    """The plain implementation of the tiny configuration's architecture."""
+    return plain_kemitar if TINY[name].get("architecture") == "Kemitar" else plain_lfm2
 
 DTYPES = ("float32", "bfloat16")
 STORED = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -42,22 +50,44 @@ def model_dir(name: str, dtype: str, seed: int = 3) -> Path:
 
 @functools.lru_cache(maxsize=None)
 def plain_model(name: str, dtype: str, seed: int = 3):
-    return P.load_model_dir(model_dir(name, dtype, seed))
+    return plain_module(name).load_model_dir(model_dir(name, dtype, seed))
 
 
 @functools.lru_cache(maxsize=None)
 def _plain_logits_cached(name, dtype, seed, tokens):
     cfg, w = plain_model(name, dtype, seed)
-    return P.forward(cfg, w, list(tokens))
+    return np.asarray(plain_module(name).forward(cfg, w, list(tokens)))
 
 
 def plain_logits(name: str, dtype: str, tokens, seed: int = 3) -> np.ndarray:
     return _plain_logits_cached(name, dtype, seed, tuple(int(t) for t in tokens))
 
 
+@functools.lru_cache(maxsize=None)
+def _rounding_error_cached(name, dtype, seed, tokens):
+    cfg, w = plain_model(name, dtype, seed)
+    plain = plain_module(name)
+    exact = np.asarray(plain.forward(cfg, w, list(tokens)))
+    rounded = np.asarray(plain.forward(cfg, w, list(tokens), rnd=plain.bf16))
+    return float(np.abs(exact - rounded).max()) / max(1.0, float(np.abs(exact).max()))
+
+
+def oracle_bound(name: str, dtype: str, tokens, seed: int = 3) -> float:
+    """The bound for the engine against the plain implementation on these tokens, relative to the
+    logits' scale.  float32: the fixed bound.  bfloat16: three times the error that rounding alone
+    causes here -- the plain implementation run once more with its products' inputs and results
+    rounded to bfloat16 -- and no less than the fixed bound.  (Only for architectures whose plain
+    implementation can round: how much rounding costs depends on the model, some configurations
+    lose ten unit roundoffs of the logit scale to it, some a few.)"""
+    if dtype != "bfloat16" or not hasattr(plain_module(name), "bf16"):
+        return TOL_ORACLE[dtype]
+    noise = _rounding_error_cached(name, dtype, seed, tuple(int(t) for t in tokens))
+    return max(TOL_ORACLE[dtype], 3.0 * noise)
+
+
 def random_tokens(name: str, length: int, seed: int) -> list:
     rng = np.random.default_rng(seed)
-    return [int(t) for t in rng.integers(0, TINY[name]["vocab_size"], size=length)]
+    return [int(t) for t in rng.integers(0, vocab_of(TINY[name]), size=length)]
 
 
 @functools.lru_cache(maxsize=None)

@@ -30,6 +30,15 @@ import torch
 F64 = torch.float64
 
 
+def same(value):
+    return value
+
+
+def bf16(value):
+    """Round to bfloat16 and widen again: what a 16-bit engine does to the results of its products."""
+    return value.to(torch.bfloat16).to(F64)
+
+
 # ------------------------------------------------------------------ files
 def read_safetensors(path) -> dict:
     """Every tensor of a safetensors file widened to float64 (8-byte length, JSON header, data)."""
@@ -102,13 +111,14 @@ def rotate_half_split(v, positions, base, dims):
     return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], dim=-1)
 
 
-def latent_and_rotated_key(h, w, prefix, m, eps):
-    """(latent [N][rank], rotated shared key part [N][rot_dim]) of the layer whose mixer is ``m``."""
+def latent_and_rotated_key(h, w, prefix, m, eps, rnd=same):
+    """(latent [N][rank], rotated shared key part [N][rot_dim]) of the layer whose mixer is ``m``.
+    ``rnd`` is applied to what a 16-bit engine would store in 16 bits (here and below)."""
     rank, rot_dim = int(m["kv_rank"]), int(m["rot_dim"])
-    d = h @ w[prefix + "mix.dkv"].T
-    latent = unit_rms(d[:, :rank], eps) * w[prefix + "mix.dkv.norm"]
+    d = rnd(h @ w[prefix + "mix.dkv"].T)
+    latent = rnd(unit_rms(d[:, :rank], eps) * w[prefix + "mix.dkv.norm"])
     positions = torch.arange(h.shape[0])
-    key_rot = rotate_half_split(d[:, rank:rank + rot_dim], positions, m["rot"]["base"], int(m["rot"]["dims"]))
+    key_rot = rnd(rotate_half_split(d[:, rank:rank + rot_dim], positions, m["rot"]["base"], int(m["rot"]["dims"])))
     return latent, key_rot
 
 
@@ -122,30 +132,33 @@ def softmax_with_sink(scores, sink):
     return weights / (weights.sum(dim=-1, keepdim=True) + torch.exp(sink[:, None, None] - top))
 
 
-def latent_attention(h, w, prefix, m, latent, key_rot):
+def latent_attention(h, w, prefix, m, latent, key_rot, rnd=same):
     """The mixer of one layer over a whole sequence, keys and values from (latent, key_rot)."""
     H, dim, rot_dim, vdim, rank = (int(m[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
     N = h.shape[0]
-    q = (h @ w[prefix + "mix.q"].T).reshape(N, H, dim + rot_dim)
+    q = rnd(h @ w[prefix + "mix.q"].T).reshape(N, H, dim + rot_dim)
     q_plain = q[..., :dim]
-    q_rot = rotate_half_split(q[..., dim:], torch.arange(N), m["rot"]["base"], int(m["rot"]["dims"]))
-    k_plain = (latent @ w[prefix + "mix.uk"].T).reshape(N, H, dim)
-    value = (latent @ w[prefix + "mix.uv"].T).reshape(N, H, vdim)
+    q_rot = rnd(rotate_half_split(q[..., dim:], torch.arange(N), m["rot"]["base"], int(m["rot"]["dims"])))
+    k_plain = rnd(latent @ w[prefix + "mix.uk"].T).reshape(N, H, dim)
+    value = rnd(latent @ w[prefix + "mix.uv"].T).reshape(N, H, vdim)
     scores = (torch.einsum("nhd,mhd->hnm", q_plain, k_plain)
               + torch.einsum("nhr,mr->hnm", q_rot, key_rot)) * float(m["scale"])
     weights = softmax_with_sink(scores, w[prefix + "mix.sink"])
-    out = torch.einsum("hnm,mhv->nhv", weights, value).reshape(N, H * vdim)
+    out = rnd(torch.einsum("hnm,mhv->nhv", rnd(weights), value).reshape(N, H * vdim))
     return out @ w[prefix + "mix.o"].T
 
 
-def gated_feed_forward(x, w, prefix):
+def gated_feed_forward(x, w, prefix, rnd=same):
     gate = x @ w[prefix + "mlp.gate"].T
-    return (gate * torch.sigmoid(gate) * (x @ w[prefix + "mlp.up"].T)) @ w[prefix + "mlp.down"].T
+    return rnd(gate * torch.sigmoid(gate) * (x @ w[prefix + "mlp.up"].T)) @ w[prefix + "mlp.down"].T
 
 
 # ------------------------------------------------------------------ the model
-def forward(cfg, w, tokens, return_layers: bool = False):
-    """Logits [N][vocab] of one whole sequence (and the stream after every layer, if asked)."""
+def forward(cfg, w, tokens, return_layers: bool = False, rnd=same):
+    """Logits [N][vocab] of one whole sequence (and the stream after every layer, if asked).
+    ``rnd=bf16`` rounds what a 16-bit engine keeps in 16 bits (inputs and results of the products, not
+    the stream, the norms or the softmax): the difference to ``rnd=same`` is the error that rounding
+    alone causes, which the tests of the 16-bit path take their bound from."""
     eps = float(cfg["norm"]["eps"])
     x = embed(tokens, w, cfg)
     kept = {}                     # layer index -> (latent, rotated key part)
@@ -155,16 +168,27 @@ def forward(cfg, w, tokens, return_layers: bool = False):
         if layer["type"] != "latent_attention":
             raise ValueError(f"plain Kemitar: unknown layer type {layer['type']!r}")
         m = layer["mixer"]
-        h = token_shift(x, w[prefix + "shift"])
+        h = rnd(token_shift(x, w[prefix + "shift"]))
         source = m.get("kv_from")
         if source is None:
-            kept[index] = latent_and_rotated_key(h, w, prefix, m, eps)
+            kept[index] = latent_and_rotated_key(h, w, prefix, m, eps, rnd)
             source = index
-        x = x + unit_rms(latent_attention(h, w, prefix, m, *kept[int(source)]), eps) * w[prefix + "norm1"]
+        x = x + unit_rms(latent_attention(h, w, prefix, m, *kept[int(source)], rnd=rnd), eps) * w[prefix + "norm1"]
         if layer.get("mlp") is not None:
             if layer["mlp"]["kind"] != "dense":
                 raise ValueError(f"plain Kemitar: unknown feed-forward {layer['mlp']['kind']!r}")
-            x = x + unit_rms(gated_feed_forward(x, w, prefix), eps) * w[prefix + "norm2"]
+            x = x + unit_rms(gated_feed_forward(rnd(x), w, prefix, rnd), eps) * w[prefix + "norm2"]
         after.append(x.clone())
-    logits = (unit_rms(x, eps) * w["final.norm"]) @ w["head"].T
+    logits = rnd(unit_rms(x, eps) * w["final.norm"]) @ w["head"].T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def greedy_generate(cfg, w, prompt, count):
+    """Greedy continuation by re-running whole sequences (the lowest id among equal logits)."""
+    tokens, out = list(prompt), []
+    for _ in range(count):
+        row = forward(cfg, w, tokens)[-1].numpy()
+        nxt = int(np.lexsort((np.arange(row.size), -row))[0])
+        out.append(nxt)
+        tokens.append(nxt)
+    return out

@@ -49,3 +49,48 @@ def make_model_dir(path, config: dict, seed: int, preset: str = "unit",
     if edit is not None:
         edit(tensors)
     return write_model_dir(path, typed.to_dict(), tensors, seed)
+
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, base, scale, kv_from=None):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+             "rot": {"base": base, "dims": rot_dim}, "scale": scale}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return mixer
+
+
+def _kemitar_layer(mixer, ff):
+    return {"type": "latent_attention", "mixer": mixer,
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+# Two tiny Kemitar configurations that differ in every size and option: head counts (1 to 20), plain /
+# rotated / value widths that are all different, latent ranks (one odd), cache rows that need padding,
+# layers that read the rows of a layer one or two places back, layers without a feed-forward, a pair
+# table of one bucket, multipliers of 1, a width that is no multiple of 8.
+KEMITAR_A = {
+    "architecture": "Kemitar", "vocab": 211, "width": 80, "norm": {"eps": 1e-6},
+    "embedding": {"scale": 3.0, "bigram": {"buckets": 97, "mul_prev": 31, "mul_cur": 5}},
+    "layers": [
+        _kemitar_layer(_latent(3, 24, 8, 16, 40, 1000.0, 0.3), 144),
+        _kemitar_layer(_latent(5, 16, 8, 24, 40, 1000.0, 0.2, kv_from=0), None),
+        _kemitar_layer(_latent(2, 8, 8, 40, 40, 1000.0, 0.5, kv_from=0), 112),
+        _kemitar_layer(_latent(2, 8, 4, 8, 20, 50.0, 0.4), 96),
+    ],
+}
+
+KEMITAR_B = {
+    "architecture": "Kemitar", "vocab": 130, "width": 82, "norm": {"eps": 1e-5},
+    "embedding": {"scale": 1.0, "bigram": {"buckets": 1, "mul_prev": 1, "mul_cur": 1}},
+    "layers": [
+        _kemitar_layer(_latent(1, 10, 6, 12, 37, 300000.0, 0.25), 50),
+        _kemitar_layer(_latent(20, 16, 16, 8, 48, 10000.0, 0.18), None),
+        _kemitar_layer(_latent(17, 12, 16, 4, 48, 10000.0, 0.22, kv_from=1), 200),
+    ],
+}
+
+TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B})
+
+
+def vocab_of(config: dict) -> int:
+    return int(config.get("vocab_size", config.get("vocab")))
