@@ -241,7 +241,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ seg_start, const int* __restrict__ tile_seg,
                          const int* __restrict__ tile_tok0, const int* __restrict__ block_table,
                          int max_pages, __nv_bfloat16* __restrict__ out, int nh, int nkv, int group,
-                         int tokens_per_tile, int window, float scale) {
+                         int tokens_per_tile, int window, float scale, const float* __restrict__ sink,
+                         int pool_nkv) {
     fwb::pdl_entry();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -285,11 +286,22 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    if (sink) {
+        // a sink: a key of score sink[head] (not scaled) whose value is zero starts the row's maximum and sum
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            if (hi[h] >= 0) {
+                m[h] = sink[head[h]] * LOG2E;
+                l[h] = 1.0f;
+            }
+    }
+    // several groups of query heads may share one head of the pool (kvh counts groups)
+    const int pool_kvh = (int)((long)kvh * pool_nkv / nkv);
 
     auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
     auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
     auto issue = [&](int tile, int s) {
-        const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+        const size_t src = ((size_t)table[tile] * pool_nkv + pool_kvh) * KEYS * HD;
         load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
         cp_async_commit();
     };
@@ -332,6 +344,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // The decode kernel may do the step's q/k norm, rotation and page write itself (a step of single
 // tokens only): it then reads the rows of the fused q|k|v projection instead of finished queries.
 struct FusedQkv {
+    const float* sink;           // [nh] or null: a score per head that joins the softmax denominator (no value)
+    int pool_nkv;                // heads of the pools; 0: nkv (else several groups of query heads share a pool head)
     const __nv_bfloat16* qkv;    // [T][(nh + 2 nkv_in) HD]; null: `q` holds finished queries
     const float* wq;             // [HD] head-norm weights (unused when !use_norm)
     const float* wk;
@@ -426,6 +440,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int tile_begin = first_tile + split * tiles_per_split;
     int tile_end = tile_begin + tiles_per_split;
     if (tile_end > last_tile + 1) tile_end = last_tile + 1;
+    const int pool_nkv = fused.pool_nkv > 0 ? fused.pool_nkv : nkv;
+    const int pool_kvh = (int)((long)kvh * pool_nkv / nkv);
 
     // cp.async: two stages, or the deep ring; TMA: as many as the launcher found room for
     const int DECODE_STAGES = TMA ? tma_stages : (DEEP ? decode_stages<HD>() : 2);
@@ -448,7 +464,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 // the stage was read (and, in a token's last tile, cleared) through ordinary loads and stores
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 tc5::mbar_expect_tx(&full_bar[s], 2 * TILE * 2);
-                const int row = (table[tile] * nkv + kvh) * KEYS;
+                const int row = (table[tile] * pool_nkv + pool_kvh) * KEYS;
 #pragma unroll
                 for (int x = 0; x < HD / 64; ++x) {
                     tc5::tma_load_2d(stage_k(s) + x * KEYS * 64, &map_k, &full_bar[s], x * 64, row);
@@ -458,7 +474,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             return;
         }
         if (tile < tile_end) {
-            const size_t src = ((size_t)table[tile] * nkv + kvh) * KEYS * HD;
+            const size_t src = ((size_t)table[tile] * pool_nkv + pool_kvh) * KEYS * HD;
             load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
         }
         cp_async_commit();                                  // an empty group keeps the count in step
@@ -496,6 +512,17 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    if (fused.sink && split == 0 && warp == 0) {
+        // the sink counts once per row: the first warp of the first slice starts from it
+        if (g < group) {
+            m[0] = fused.sink[kvh * group + g] * LOG2E;
+            l[0] = 1.0f;
+        }
+        if (g + 8 < group) {
+            m[1] = fused.sink[kvh * group + g + 8] * LOG2E;
+            l[1] = 1.0f;
+        }
+    }
 
     for (; issued < DECODE_STAGES - 1; ++issued) issue(tile_begin + issued, issued);
     for (int tile = tile_begin; tile < tile_end; ++tile) {
@@ -676,14 +703,15 @@ template <int HD>
 int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                    const int* seg_start, const int* tile_seg, const int* tile_tok0, const int* block_table,
                    int max_pages, void* out, int n_tiles, int nh, int nkv, int tokens_per_tile, int window,
-                   float scale, cudaStream_t stream) {
+                   float scale, const float* sink, int pool_nkv, cudaStream_t stream) {
     auto kernel = attention_prefill_kernel<HD>;
     int st = opt_in_smem(kernel, Smem<HD>::BYTES);
     if (st != FWB_OK) return st;
     using bf = __nv_bfloat16;
     fwb::pdl(kernel, dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, seg_start, tile_seg, tile_tok0,
-        block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale * LOG2E);
+        block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale * LOG2E, sink,
+        pool_nkv > 0 ? pool_nkv : nkv);
     return fwb_launch_status();
 }
 
@@ -776,7 +804,7 @@ int launch_decode(const void* q, const void* k_pool, const void* v_pool, const i
     memset(&map_k, 0, sizeof(map_k));
     memset(&map_v, 0, sizeof(map_v));
     if constexpr (HD == 64 || HD == 128) {
-        const long pool_rows = (long)num_pages * nkv * KEYS;
+        const long pool_rows = (long)num_pages * (fused.pool_nkv > 0 ? fused.pool_nkv : nkv) * KEYS;
         const bool aligned = ((((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15) == 0;
         if (g_decode_tma && num_pages > 0 && aligned && pool_rows <= 2147483647L &&
             tc5::make_map(&map_k, k_pool, pool_rows, HD, KEYS) && tc5::make_map(&map_v, v_pool, pool_rows, HD, KEYS))
@@ -812,6 +840,29 @@ bool shape_ok(int nh, int nkv, int hd, int page_size) {
 // Prompt portions (and anything else): q, out [T][nh*hd] bf16; pools [pages][nkv][64][hd] bf16.
 // tile_seg, tile_tok0: [n_tiles], a tile holds up to `tokens_per_tile` = 64 / group consecutive
 // tokens of one segment.
+// The general form.  sink: fp32 [nh] or null -- a score per head (not scaled) that joins the row's
+// softmax denominator and has no value.  pool_nkv: heads the pools have (0: nkv); with fewer than
+// nkv, nkv counts groups of nh / nkv query heads and group i reads pool head i * pool_nkv / nkv
+// (one latent row per token shared by every head: pool_nkv = 1).  v_pool may be k_pool.
+FWB_API int fwb_attention_prefill_mma_sink(const void* q, const void* k_pool, const void* v_pool,
+                                           const int* positions, const int* seg_start, const int* tile_seg,
+                                           const int* tile_tok0, const int* block_table, int max_pages,
+                                           int page_size, void* out, int n_tiles, int nh, int nkv, int hd,
+                                           int tokens_per_tile, int window, float scale, const float* sink,
+                                           int pool_nkv, cudaStream_t stream) {
+    if (n_tiles <= 0) return FWB_OK;
+    if (!q || !k_pool || !v_pool || !positions || !seg_start || !tile_seg || !tile_tok0 || !block_table || !out)
+        return FWB_BAD_ARGUMENT;
+    if (!shape_ok(nh, nkv, hd, page_size)) return FWB_UNSUPPORTED;
+    if (pool_nkv < 0 || pool_nkv > nkv || (pool_nkv > 0 && nkv % pool_nkv)) return FWB_BAD_ARGUMENT;
+    if (tokens_per_tile < 1 || tokens_per_tile * (nh / nkv) > 64) return FWB_BAD_ARGUMENT;
+#define CALL(HD)                                                                                          \
+    launch_prefill<HD>(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table, max_pages, \
+                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, sink, pool_nkv, stream)
+    FWB_HD_SWITCH(hd, CALL)
+#undef CALL
+}
+
 FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool,
                                       const int* positions, const int* seg_start, const int* tile_seg,
                                       const int* tile_tok0, const int* block_table, int max_pages,
@@ -824,7 +875,7 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
     if (tokens_per_tile < 1 || tokens_per_tile * (nh / nkv) > 64) return FWB_BAD_ARGUMENT;
 #define CALL(HD)                                                                                          \
     launch_prefill<HD>(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table, max_pages, \
-                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, stream)
+                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, nullptr, 0, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
 }
@@ -834,24 +885,38 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
 // while the launch has few CTAs) or by a second kernel through scratch: part_o needs
 // T*nkv*splits*group*hd floats and part_ml T*nkv*splits*group*2 floats.  num_pages: the pools'
 // first extent (0: unknown, no TMA).
+FWB_API int fwb_attention_decode_mma_sink(const void* q, const void* k_pool, const void* v_pool,
+                                          const int* positions, const int* tok_seg, const int* block_table,
+                                          int max_pages, int page_size, int num_pages, void* out, float* part_o,
+                                          float* part_ml, int T, int nh, int nkv, int hd, int splits,
+                                          int tiles_per_split, int window, float scale, int merge_in_cluster,
+                                          const float* sink, int pool_nkv, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
+    if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
+    if (pool_nkv < 0 || pool_nkv > nkv || (pool_nkv > 0 && nkv % pool_nkv)) return FWB_BAD_ARGUMENT;
+    const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
+    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
+    FusedQkv fused;
+    memset(&fused, 0, sizeof(fused));
+    fused.sink = sink;
+    fused.pool_nkv = pool_nkv;
+#define CALL(HD)                                                                                          \
+    launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o,  \
+                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, fused, stream)
+    FWB_HD_SWITCH(hd, CALL)
+#undef CALL
+}
+
 FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool,
                                      const int* positions, const int* tok_seg, const int* block_table,
                                      int max_pages, int page_size, int num_pages, void* out, float* part_o,
                                      float* part_ml, int T, int nh, int nkv, int hd, int splits,
                                      int tiles_per_split, int window, float scale, int merge_in_cluster,
                                      cudaStream_t stream) {
-    if (T <= 0) return FWB_OK;
-    if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
-    if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
-    const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
-    if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
-    FusedQkv fused;
-    memset(&fused, 0, sizeof(fused));
-#define CALL(HD)                                                                                          \
-    launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o,  \
-                      part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, fused, stream)
-    FWB_HD_SWITCH(hd, CALL)
-#undef CALL
+    return fwb_attention_decode_mma_sink(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, page_size,
+                                         num_pages, out, part_o, part_ml, T, nh, nkv, hd, splits, tiles_per_split,
+                                         window, scale, merge_in_cluster, nullptr, 0, stream);
 }
 
 // The same for a step of single tokens only, with the q/k head norm, the rotation and the page write
@@ -879,6 +944,8 @@ FWB_API int fwb_attention_decode_fused(const void* qkv, int nkv_in, const float*
     const bool in_cluster = merge_in_cluster != 0 && splits <= 8;
     if (splits < 1 || tiles_per_split < 1 || (splits > 1 && !in_cluster && (!part_o || !part_ml))) return FWB_BAD_ARGUMENT;
     FusedQkv fused;
+    fused.sink = nullptr;
+    fused.pool_nkv = 0;
     fused.qkv = static_cast<const __nv_bfloat16*>(qkv);
     fused.wq = wq;
     fused.wk = wk;

@@ -78,6 +78,7 @@ struct AttnParams {
     int max_pages, nh, nkv, group, tokens_per_tile, window, n_row_tiles;
     int items_per_cta;           // 2: CTA c takes items c and n-1-c; 1: one item each (few items)
     float scale_log2;            // softmax scale * log2(e)
+    const float* sink;           // [nh] or null: a score per head (not scaled) in the softmax denominator, no value
     int* status;
 };
 
@@ -313,6 +314,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             // only when that has moved by more than RESCALE_STEP (in base 2), so P stays below
             // 2^RESCALE_STEP and O, which accumulates in tensor memory, is rescaled rarely.
             float m = -INFINITY, l = 0.0f;
+            if (prm.sink && valid) {
+                // the sink starts the row: a key of score sink[head] whose value is zero
+                m = prm.sink[head] * LOG2E;
+                l = 1.0f;
+            }
             // the highest lower bound of the keys any row of this item may see
             const int lo_max = prm.window > 0 ? (item.pos_last - prm.window + 1 > 0 ? item.pos_last - prm.window + 1 : 0) : 0;
             for (int j = 0; j < item.n_tiles; ++j) {
@@ -461,12 +467,32 @@ FWB_API int fwb_attention_prefill_tcgen05_accepts(int nh, int nkv, int hd, int p
 
 // q, out: [T][nh*hd] bf16.  k_pool, v_pool: [num_pages][nkv][64][hd] bf16.  tile_seg, tile_tok0:
 // [n_tiles]; a tile holds up to `tokens_per_tile` (<= 128 / group) consecutive tokens of one segment.
+FWB_API int fwb_attention_prefill_tcgen05_sink(const void* q, const void* k_pool, const void* v_pool,
+                                               const int* positions, const int* seg_start, const int* tile_seg,
+                                               const int* tile_tok0, const int* block_table, int max_pages,
+                                               int page_size, int num_pages, void* out, int n_tiles, int nh,
+                                               int nkv, int hd, int tokens_per_tile, int window, float scale,
+                                               const float* sink, cudaStream_t stream);
+
 FWB_API int fwb_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool,
                                           const int* positions, const int* seg_start, const int* tile_seg,
                                           const int* tile_tok0, const int* block_table, int max_pages,
                                           int page_size, int num_pages, void* out, int n_tiles, int nh,
                                           int nkv, int hd, int tokens_per_tile, int window, float scale,
                                           cudaStream_t stream) {
+    return fwb_attention_prefill_tcgen05_sink(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0,
+                                              block_table, max_pages, page_size, num_pages, out, n_tiles, nh, nkv,
+                                              hd, tokens_per_tile, window, scale, nullptr, stream);
+}
+
+// The same with a sink: fp32 [nh] or null, a score per head that joins every row's softmax denominator
+// (not scaled, no value).  v_pool may be k_pool (a row that serves as key and as value).
+FWB_API int fwb_attention_prefill_tcgen05_sink(const void* q, const void* k_pool, const void* v_pool,
+                                               const int* positions, const int* seg_start, const int* tile_seg,
+                                               const int* tile_tok0, const int* block_table, int max_pages,
+                                               int page_size, int num_pages, void* out, int n_tiles, int nh,
+                                               int nkv, int hd, int tokens_per_tile, int window, float scale,
+                                               const float* sink, cudaStream_t stream) {
     if (n_tiles <= 0) return FWB_OK;
     if (!q || !k_pool || !v_pool || !positions || !seg_start || !tile_seg || !tile_tok0 || !block_table || !out)
         return FWB_BAD_ARGUMENT;
@@ -498,6 +524,7 @@ FWB_API int fwb_attention_prefill_tcgen05(const void* q, const void* k_pool, con
     // triangle when there are waves of them; up to one wave of single items, single items finish sooner
     prm.items_per_cta = (long)n_tiles * nkv <= 148 ? 1 : 2;
     prm.scale_log2 = scale * LOG2E;
+    prm.sink = sink;
     prm.status = status_word();
     return hd == 64 ? launch<64>(map_k, map_v, prm, n_tiles, stream)
                     : launch<128>(map_k, map_v, prm, n_tiles, stream);

@@ -148,11 +148,37 @@ def fused_decode_attention(ctx, qkv, cache, block_table, n_heads, n_kv_in, windo
                                       n_heads, window, scale, splits, tiles_per_split, in_cluster)
 
 
-def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype):
-    """Causal GQA of every token of the step over its request's pages."""
+def head_groups(n_heads: int, n_kv: int):
+    """In how many groups the tensor-core kernels take the query heads (a group is at most 16 heads that
+    read one pool head): ``n_kv`` when that fits, else the fewest groups per pool head that divide its
+    heads evenly -- several groups then share a pool head.  None: no such cut."""
+    if n_kv <= 0 or n_heads % n_kv:
+        return None
+    per = n_heads // n_kv
+    for cut in range(1, per + 1):
+        if per % cut == 0 and per // cut <= 16:
+            return n_kv * cut
+    return None
+
+
+def tensor_core_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tensor-core kernels take this shape, the query heads cut into ``head_groups``."""
+    groups = head_groups(n_heads, n_kv)
+    return groups is not None and ops.attention_mma_shape_ok(n_heads, groups, head_dim, page_size)
+
+
+def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype, sink=None):
+    """Causal GQA of every token of the step over its request's pages.  A cache with one pool
+    (``v_pool`` None) holds rows that serve as keys and as values.  ``sink``: fp32 [n_heads], a score
+    per head that joins every softmax denominator (not scaled, no value)."""
     batch = ctx.batch
-    k_pool, v_pool = cache.k_pool, cache.v_pool
-    _, n_kv, page_size, head_dim = k_pool.shape
+    k_pool = cache.k_pool
+    v_pool = cache.v_pool if cache.v_pool is not None else k_pool
+    _, pool_heads, page_size, head_dim = k_pool.shape
+    n_kv = head_groups(n_heads, pool_heads) or pool_heads      # groups of query heads, as the kernels count them
+    extra = {}
+    if sink is not None or n_kv != pool_heads:
+        extra = {"sink": sink, "groups": n_kv}
     if (_use_mma and q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
             and out_dtype == torch.bfloat16
             and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
@@ -160,7 +186,7 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1], head_dim)
             return ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg,
                                             block_table, n_heads, window, scale, splits,
-                                            tiles_per_split, in_cluster)
+                                            tiles_per_split, in_cluster, **extra)
         group = n_heads // n_kv
         out = None
         first = 0
@@ -173,19 +199,26 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             splits, tiles_per_split, in_cluster = decode_splits(first, n_kv, block_table.shape[1], head_dim)
             ops.attention_decode_mma(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
                                      n_heads, window, scale, splits, tiles_per_split, in_cluster,
-                                     out=out, n_tokens=first)
-        if (_use_tcgen05 and not _force_tiled and ops.attention_tcgen05_shape_ok(n_heads, n_kv, head_dim, page_size)
-                and 2 * batch.max_segment * group >= 128):
+                                     out=out, n_tokens=first, **extra)
+        # the tcgen05 kernel takes up to 128 query heads per pool head in one tile: no cut into groups
+        wide = n_heads // pool_heads
+        if (_use_tcgen05 and not _force_tiled
+                and ops.attention_tcgen05_shape_ok(n_heads, pool_heads, head_dim, page_size)
+                and 2 * batch.max_segment * wide >= 128):
             # prompt portions that fill at least half of a 128-row tile: S and PV in tensor memory
-            tokens_per_tile = max(1, 128 // group)
+            tokens_per_tile = max(1, 128 // wide)
             tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile, first)
             return ops.attention_prefill_tcgen05(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                                  tile_seg, tile_tok0, n_tiles, tokens_per_tile,
-                                                 block_table, n_heads, window, scale, out=out)
+                                                 block_table, n_heads, window, scale, out=out,
+                                                 **({"sink": sink} if sink is not None else {}))
         tokens_per_tile = max(1, 64 // group)
         tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile, first)
         return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                          tile_seg, tile_tok0, n_tiles, tokens_per_tile, block_table,
-                                         n_heads, window, scale, out=out)
+                                         n_heads, window, scale, out=out, **extra)
+    if sink is not None or cache.v_pool is None:
+        raise lib.KernelError("this attention shape has no tensor-core kernel, and the fp32 kernel takes "
+                              "neither a sink nor rows that are key and value at once")
     return ops.attention_simt(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
                               n_heads, window, scale, out_dtype)

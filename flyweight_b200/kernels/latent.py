@@ -1,6 +1,7 @@
 """Python faces of the kernels behind the latent-attention mixer, the token shift, the hashed
 pair embedding and the gain-only output norm (``csrc/latent_attention.cu``,
-``csrc/latent_attention_mma.cu``, ``csrc/stream_mix.cu``)."""
+``csrc/head_linear_mma.cu``, ``csrc/stream_mix.cu``).  The bfloat16 attention itself runs on the
+engine's paged attention kernels (``kernels/attention.py``): the cached row is key and value at once."""
 from __future__ import annotations
 
 from typing import Optional
@@ -99,7 +100,7 @@ def latent_prepare(proj: torch.Tensor, kv_col: int, norm_w: Optional[torch.Tenso
     return qa
 
 
-_mma_enabled = False
+_mma_enabled = True
 
 
 def set_tensor_cores(flag: bool) -> None:
@@ -107,6 +108,10 @@ def set_tensor_cores(flag: bool) -> None:
     (on by default) or the fp32-FMA kernels for everything."""
     global _mma_enabled
     _mma_enabled = bool(flag)
+
+
+def tensor_cores() -> bool:
+    return _mma_enabled
 
 
 def head_linear(x: torch.Tensor, x_col: int, x_head: int, in_features: int, w: torch.Tensor,
@@ -123,8 +128,8 @@ def head_linear(x: torch.Tensor, x_col: int, x_head: int, in_features: int, w: t
         raise KernelError("per-head product: a head lies outside its row")
     size = x.element_size()
     x_ptr, y_ptr = x.data_ptr() + x_col * size, y.data_ptr() + y_col * size
-    if (_mma_enabled and x.dtype == torch.bfloat16 and K % 16 == 0 and N % 8 == 0
-            and all(v % 2 == 0 for v in (x.shape[1], x_col, x_head, y.shape[1], y_col, y_head))):
+    if (_mma_enabled and x.dtype == torch.bfloat16
+            and all(v % 2 == 0 for v in (N, K, x.shape[1], x_col, x_head, y.shape[1], y_col, y_head))):
         lib.call("fwb_head_linear_mma", x_ptr, ptr(w), y_ptr, x.shape[0], N, K, heads, c_longlong(x.shape[1]),
                  c_longlong(x_head), c_longlong(y.shape[1]), c_longlong(y_head), stream())
         return

@@ -13,11 +13,18 @@ row ``(U_h^T q_plain | q_rot)`` of the cache row's layout, attention runs betwee
 and the one cached row per token, with the row's first ``rank`` columns as values, and V_h is
 applied to the weighted sum of latents afterwards.  Nothing per head is ever built for a cached
 token, whether the step is a whole prompt, a portion or one token.
+
+In bfloat16 that attention is the engine's paged attention with one pool head that every query head
+reads and that serves as key and as value (tcgen05 for prompt portions, the split-context kernel for
+single tokens), so the cached row is padded to a head size those kernels have (64 or 128 entries when
+it fits, which gives prompts the tcgen05 kernel); the per-head products run on tensor cores too.
+Rows longer than 128 entries, and the 32-bit path, run the fp32 kernel of ``csrc/latent_attention.cu``.
 """
 from __future__ import annotations
 
 import torch
 
+from ..kernels import attention as attention_kernels
 from ..kernels import latent as latent_kernels
 from ..kernels import ops
 from ..weights.loader import TensorDecl
@@ -55,8 +62,10 @@ class LatentAttention(Mixer):
             raise ValueError(f"{self.position.rotary_dim} turning channels but a rotated part of {self.rot}")
         if min(self.n_heads, self.dim, self.vdim, self.rank) <= 0 or self.rot < 0:
             raise ValueError("latent attention: heads, dim, vdim and kv_rank must be positive")
-        # a cache row: latent, turned key part, zero padding up to a multiple of 16 entries
-        self.row = _round_up(self.rank + self.rot, 16)
+        # a cache row: latent, turned key part, zero padding up to a multiple of 16 entries -- up to 64 or
+        # 128 where that is near: the head sizes that every tensor-core attention kernel takes
+        used = self.rank + self.rot
+        self.row = 64 if used <= 64 else (128 if 96 < used <= 128 else _round_up(used, 16))
         self.q_width = self.n_heads * (self.dim + self.rot)
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = self.sink = None
 
@@ -125,8 +134,18 @@ class LatentAttention(Mixer):
             self.rank, self.row, self.eps)
         qa2 = qa.view(qa.shape[0], self.n_heads * self.row)
         latent_kernels.head_linear(proj, 0, self.dim + self.rot, self.dim, self.w_uk_t, qa2, 0, self.row)
-        mixed = latent_kernels.latent_attention(qa, cache.k_pool, self.sink, batch, block_table, self.rank,
-                                                self.rank + self.rot, self.scale)
+        pool = cache.k_pool
+        if (act == torch.bfloat16 and pool.dtype == torch.bfloat16 and latent_kernels.tensor_cores()
+                and attention_kernels.tensor_core_shape_ok(self.n_heads, 1, self.row, pool.shape[2])):
+            # many query heads over one pool head whose rows are keys and values: the paged attention
+            # kernels; the weighted rows come back [T][heads][row], their first `rank` entries count
+            mixed = attention_kernels.paged_attention(ctx, qa2, cache, block_table, self.n_heads, 0, self.scale,
+                                                      act, sink=self.sink)
+            stride = self.row
+        else:
+            mixed = latent_kernels.latent_attention(qa, pool, self.sink, batch, block_table, self.rank,
+                                                    self.rank + self.rot, self.scale)
+            stride = self.rank
         heads_out = torch.empty((mixed.shape[0], self.n_heads * self.vdim), dtype=act, device=mixed.device)
-        latent_kernels.head_linear(mixed, 0, self.rank, self.rank, self.w_uv, heads_out, 0, self.vdim)
+        latent_kernels.head_linear(mixed, 0, stride, self.rank, self.w_uv, heads_out, 0, self.vdim)
         return ops.linear(heads_out, self.w_o, torch.float32)

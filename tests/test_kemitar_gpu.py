@@ -66,7 +66,7 @@ def test_unequal_requests_in_one_batch_over_a_small_pool(name, dtype):
     for rid, ids in tokens.items():
         assert_close(got[rid], plain_logits(name, dtype, ids), oracle_bound(name, dtype, ids),
                      f"{name} {dtype} request {rid}")
-    assert runner.cache.groups[0].pool.in_use == 0
+    assert runner.cache.groups[0].pool.n_used == 0
     runner.check_health()
 
 

@@ -323,6 +323,21 @@ def test_one_key_that_stands_out_is_found_wherever_it_lies(dtype, far):
         out = latent.latent_attention(dev(qa, dtype), dev(pool, dtype), dev(sink, torch.float32), batch,
                                       batch.block_tables[0], rank, rank + rot, scale)
         close(out.view(new, heads, -1)[-1, :, :rank], want, rel, f"key {far}, {new} new tokens")
+        if dtype == torch.bfloat16:
+            # the same through the paged attention kernels (the row is key and value at once)
+            from flyweight_b200.engine import StepContext
+            from flyweight_b200.kernels import attention
+            cache = type("Cache", (), {})()
+            cache.k_pool, cache.v_pool = dev(pool, dtype), None
+            for tiled in (False, True):
+                attention.force_tiled(tiled)
+                try:
+                    out = attention.paged_attention(StepContext(batch, None, DEV), dev(qa, dtype).view(new, -1), cache,
+                                                    batch.block_tables[0], heads, 0, scale, dtype,
+                                                    sink=dev(sink, torch.float32))
+                finally:
+                    attention.force_tiled(False)
+                close(out.view(new, heads, -1)[-1, :, :rank], want, rel, f"key {far}, {new} new tokens, paged")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -365,3 +380,48 @@ def test_per_head_products(dtype, T, heads, N, K):
     got = y[:, y_col:y_col + heads * y_head].reshape(T, heads, y_head).float().cpu()
     close(got[:, :, :N], want, 1e-5 if dtype == torch.float32 else 2.0 ** -7, "products")
     assert float((got[:, :, N:] - 7.0).abs().max()) == 0.0 and float((y[:, :y_col].float() - 7.0).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("heads,row", [(8, 128), (20, 64), (17, 48), (40, 128), (128, 64)])
+@pytest.mark.parametrize("new", [1, 3, 70, 200])
+def test_paged_attention_with_a_sink_and_one_shared_pool_head(heads, row, new):
+    """Many query heads over one pool head whose rows are keys and values, with a sink per head: the
+    tensor-core kernels (decode, tiled, tcgen05 -- whichever the step's shape selects) against the
+    softmax written out."""
+    from flyweight_b200.engine import StepContext
+    from flyweight_b200.kernels import attention
+    g = torch.Generator().manual_seed(heads + new)
+    cached = [330, new, 129 + new]
+    news = [new, new, 1]
+    scale = 0.3
+    seqs = [bf16_round(torch.randn(n, row, generator=g, dtype=F64) * 0.7) for n in cached]
+    sink = torch.randn(heads, generator=g, dtype=F64) * 2.0
+    order = torch.randperm(20, generator=g).tolist()
+    pool = torch.full((20, 1, 64, row), float("nan"), dtype=F64)
+    table = torch.full((3, 6), -1, dtype=torch.int32)
+    for s, keys in enumerate(seqs):
+        for i in range(-(-keys.shape[0] // 64)):
+            page = order.pop()
+            table[s, i] = page
+            chunk = keys[i * 64:(i + 1) * 64]
+            pool[page, 0, :chunk.shape[0]] = chunk
+    # single tokens lead the batch, as the scheduler orders a mixed step
+    idx = [2, 0, 1]
+    batch = make_batch([cached[i] for i in idx], [news[i] for i in idx], table=table[idx])
+    q = bf16_round(torch.randn(sum(news), heads, row, generator=g, dtype=F64))
+    cache = type("Cache", (), {})()
+    cache.k_pool, cache.v_pool = dev(pool, torch.bfloat16), None
+    out = attention.paged_attention(StepContext(batch, None, DEV), dev(q, torch.bfloat16).view(sum(news), -1), cache,
+                                    batch.block_tables[0], heads, 0, scale, torch.bfloat16,
+                                    sink=dev(sink, torch.float32)).view(sum(news), heads, row).float().cpu().to(F64)
+    at = 0
+    for i in idx:
+        keys, n, m = seqs[i], cached[i], news[i]
+        for j in range(m):
+            pos = n - m + j
+            scores = (q[at + j] @ keys[:pos + 1].T) * scale                 # [heads][pos + 1]
+            top = torch.maximum(scores.max(dim=1).values, sink)
+            p = torch.exp(scores - top[:, None])
+            want = (p @ keys[:pos + 1]) / (p.sum(dim=1) + torch.exp(sink - top))[:, None]
+            close(out[at + j], want, 2.0 ** -7, f"sequence {i} position {pos}")
+        at += m
