@@ -41,6 +41,35 @@ LFM2_350M = dict(LFM2_1P2B, hidden_size=1024, num_attention_heads=16, intermedia
 LFM2_2P6B = dict(LFM2_1P2B, num_hidden_layers=30, full_attn_idxs=[2, 6, 10, 14, 18, 21, 24, 27],
                  intermediate_size=10752)
 MODELS = {"lfm2-350m": LFM2_350M, "lfm2-1.2b": LFM2_1P2B, "lfm2-2.6b": LFM2_2P6B}
+
+
+def kemitar_like(lfm2: dict, ff: int) -> dict:
+    """A Kemitar configuration with the layer sizes of an LFM2 one (width, depth, query heads, feed-forward
+    width, vocabulary): per head 64 plain and 32 rotated query channels and 64 value channels, a latent
+    of 96 entries (a cache row of 96 + 32 = 128), every second layer reading the rows of the one before."""
+    heads = lfm2["num_attention_heads"]
+    layers = []
+    for index in range(lfm2["num_hidden_layers"]):
+        mixer = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "scale": 96 ** -0.5,
+                 "rot": {"base": 1000000.0, "dims": 32}}
+        if index % 2:
+            mixer["kv_from"] = index - 1
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Kemitar", "vocab": lfm2["vocab_size"], "width": lfm2["hidden_size"],
+            "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
+            "layers": layers}
+
+
+# Kemitar beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what LFM2's rule
+# makes of ``intermediate_size`` at these sizes.
+KEMITAR = {"kemitar-350m": ("lfm2-350m", 4608), "kemitar-1.2b": ("lfm2-1.2b", 8192)}
+for _name, (_twin, _ff) in KEMITAR.items():
+    MODELS[_name] = kemitar_like(MODELS[_twin], _ff)
+
+
+def vocab_of(config: dict) -> int:
+    return int(config["vocab_size"] if "vocab_size" in config else config["vocab"])
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -129,8 +158,10 @@ def kv_bytes_per_token(model) -> int:
     total = 0
     for entry in model.spec.schedule:
         spec = model.layers[entry.layer].state_spec() if entry.cache_of is None else None
-        if spec is not None and hasattr(spec, "n_kv_heads"):
-            total += 2 * spec.n_kv_heads * spec.head_dim * model.precision.cache_dtype.itemsize
+        for member in (spec if isinstance(spec, tuple) else (spec,)):
+            if member is not None and hasattr(member, "n_kv_heads"):
+                pools = 2 if getattr(member, "values", True) else 1
+                total += pools * member.n_kv_heads * member.head_dim * model.precision.cache_dtype.itemsize
     return total
 
 
@@ -386,6 +417,49 @@ def run_sizes(args) -> int:
     return 0
 
 
+def run_compare(args) -> int:
+    """``--compare kemitar-350m|kemitar-1.2b``: Kemitar with random weights beside LFM2 at equal layer
+    sizes, both through the same step function -- prompts of 512, 2,048 and 8,192 tokens in one step
+    (tokens/s and TFLOP/s of the model's own flop count) and decode steps at batch 1, 8 and 64 over 4,096
+    cached tokens (tokens/s, and the bytes a step must read against the measured copy bandwidth).  One
+    JSON line per model; the LFM2 line's ffn width is checked to be the one the Kemitar twin was given."""
+    import torch
+    from flyweight_b200.engine.runtime import Model
+    if args.compare not in KEMITAR:
+        print(json.dumps({"error": f"--compare wants one of {sorted(KEMITAR)}"}))
+        return 1
+    peaks = read_peaks()
+    twin, ff = KEMITAR[args.compare]
+    for name in (args.compare, twin):
+        config = dict(MODELS[name])
+        model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
+        if name == twin and model.config.ffn_dim != ff:
+            print(json.dumps({"error": f"{twin} has a feed-forward of {model.config.ffn_dim}, {args.compare} of {ff}"}))
+            return 1
+        vocab = vocab_of(config)
+        line = {"compare": args.compare, "model": name, "parameters": model.parameter_count(),
+                "cache_bytes_per_token": kv_bytes_per_token(model), "of": peaks["source"], "prefill": {}, "decode": {}}
+        for n_tokens in (512, 2048, 8192):
+            ms = time_prefill(model, n_tokens, vocab)
+            flops = (model_flops_per_token(model) * n_tokens + attention_flops(model, n_tokens)
+                     + 2.0 * model.head.numel())
+            line["prefill"][str(n_tokens)] = {
+                "ms": round(ms, 3), "tokens_per_s": round(n_tokens / (ms / 1e3)),
+                "tflops": round(flops / (ms / 1e3) / 1e12, 1),
+                "frac": round(flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 3)}
+        for batch in (1, 8, 64):
+            timed = time_decode(model, batch, CONTEXT, args.steps, args.warmup, vocab)
+            step_bytes = model.weight_bytes(with_embedding_rows=batch) + batch * CONTEXT * kv_bytes_per_token(model)
+            line["decode"][f"b{batch}"] = {
+                "ms_per_step": round(timed["ms_per_step"], 4), "tokens_per_s": round(timed["tokens_per_s"]),
+                "gb_per_step": round(step_bytes / 1e9, 3),
+                "frac": round(step_bytes / (timed["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)}
+        print(json.dumps(line), flush=True)
+        del model
+        torch.cuda.empty_cache()
+    return 0
+
+
 def run_prefill_lengths(args) -> int:
     """One prompt of each given length through one step (``--prefill-lengths 128,512,8192``): a
     JSON line per length, the timer and the flop count of the default run's prefill figure."""
@@ -574,7 +648,7 @@ def run_kernel_times(args) -> int:
         return 1
     config = dict(MODELS[name])
     model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
-    vocab = config["vocab_size"]
+    vocab = vocab_of(config)
     rng = torch.Generator().manual_seed(0)
     if what == "decode":
         total = context + 16
@@ -667,6 +741,8 @@ def main() -> int:
     parser.add_argument("--mixed", default=None, metavar="MODEL",
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
+    parser.add_argument("--compare", default=None, metavar="MODEL",
+                        help="kemitar-350m or kemitar-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
     parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode[@BATCHxCONTEXT]|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()
@@ -678,6 +754,8 @@ def main() -> int:
         return run_profile_step(args)
     if args.kernel_times:
         return run_kernel_times(args)
+    if args.compare:
+        return run_compare(args)
     if args.mixed:
         return run_mixed(args)
     if args.sizes:

@@ -90,16 +90,18 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
     return tile + (chunk >> 3) * (KEYS * 64) + key * 64 + (((chunk & 7) ^ (key & 7)) << 3);
 }
 
-// Copy one (page, kv head) tile of K and of V into shared memory (whole CTA).
+// Copy one (page, kv head) tile of K and of V into shared memory (whole CTA).  `with_v` false: the
+// rows are keys and values at once and the value tile is the key tile itself.
 template <int HD>
 __device__ __forceinline__ void load_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
                                           const __nv_bfloat16* __restrict__ k_pool,
-                                          const __nv_bfloat16* __restrict__ v_pool, size_t src) {
+                                          const __nv_bfloat16* __restrict__ v_pool, size_t src,
+                                          bool with_v = true) {
     constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per row
     for (int i = threadIdx.x; i < KEYS * CHUNKS; i += WARPS * 32) {
         const int r = i / CHUNKS, c = i - r * CHUNKS;
         cp_async16(ks + r * Smem<HD>::ROW + c * 8, k_pool + src + (size_t)r * HD + c * 8);
-        cp_async16(vs + r * Smem<HD>::ROW + c * 8, v_pool + src + (size_t)r * HD + c * 8);
+        if (with_v) cp_async16(vs + r * Smem<HD>::ROW + c * 8, v_pool + src + (size_t)r * HD + c * 8);
     }
 }
 
@@ -298,11 +300,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     // several groups of query heads may share one head of the pool (kvh counts groups)
     const int pool_kvh = (int)((long)kvh * pool_nkv / nkv);
 
+    // one pool for keys and values (a row is both): one tile serves as both, nothing is loaded twice
+    // (the rows cleared past the last key are keys nobody may see)
+    const bool same = k_pool == v_pool;
     auto stage_k = [&](int s) { return smem + s * 2 * Smem<HD>::TILE; };
-    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + Smem<HD>::TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * Smem<HD>::TILE + (same ? 0 : Smem<HD>::TILE); };
     auto issue = [&](int tile, int s) {
         const size_t src = ((size_t)table[tile] * pool_nkv + pool_kvh) * KEYS * HD;
-        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+        load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src, !same);
         cp_async_commit();
     };
     issue(tile_begin, 0);
@@ -448,8 +453,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     constexpr int TILE = TMA ? KEYS * HD : Smem<HD>::TILE;  // elements of one K or V tile in shared memory
     // A ring of DECODE_STAGES key/value tiles: a slice of eight tiles has half of its bytes in
     // flight from the start (two stages left the memory pipe waiting on every tile's round trip).
+    // one pool for keys and values (a row is both): the key tile is the value tile, loaded once
+    const bool same = k_pool == v_pool;
     auto stage_k = [&](int s) { return smem + s * 2 * TILE; };
-    auto stage_v = [&](int s) { return smem + s * 2 * TILE + TILE; };
+    auto stage_v = [&](int s) { return smem + s * 2 * TILE + (same ? 0 : TILE); };
     if (TMA) {
         if (threadIdx.x == 0) {
             for (int s = 0; s < DECODE_STAGES; ++s) tc5::mbar_init(&full_bar[s], 1);
@@ -463,19 +470,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (threadIdx.x == 0 && tile < tile_end) {
                 // the stage was read (and, in a token's last tile, cleared) through ordinary loads and stores
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                tc5::mbar_expect_tx(&full_bar[s], 2 * TILE * 2);
+                tc5::mbar_expect_tx(&full_bar[s], (same ? 1 : 2) * TILE * 2);
                 const int row = (table[tile] * pool_nkv + pool_kvh) * KEYS;
 #pragma unroll
                 for (int x = 0; x < HD / 64; ++x) {
                     tc5::tma_load_2d(stage_k(s) + x * KEYS * 64, &map_k, &full_bar[s], x * 64, row);
-                    tc5::tma_load_2d(stage_v(s) + x * KEYS * 64, &map_v, &full_bar[s], x * 64, row);
+                    if (!same) tc5::tma_load_2d(stage_v(s) + x * KEYS * 64, &map_v, &full_bar[s], x * 64, row);
                 }
             }
             return;
         }
         if (tile < tile_end) {
             const size_t src = ((size_t)table[tile] * pool_nkv + pool_kvh) * KEYS * HD;
-            load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src);
+            load_tile<HD>(stage_k(s), stage_v(s), k_pool, v_pool, src, !same);
         }
         cp_async_commit();                                  // an empty group keeps the count in step
     };

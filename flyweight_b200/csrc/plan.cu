@@ -52,6 +52,29 @@ int fwb_attention_prefill_tcgen05(const void*, const void*, const void*, const i
 int fwb_attention_decode_mma(const void*, const void*, const void*, const int*, const int*, const int*, int,
                              int, int, void*, float*, float*, int, int, int, int, int, int, int, float, int,
                              cudaStream_t);
+int fwb_attention_prefill_mma_sink(const void*, const void*, const void*, const int*, const int*, const int*,
+                                   const int*, const int*, int, int, void*, int, int, int, int, int, int, float,
+                                   const float*, int, cudaStream_t);
+int fwb_attention_prefill_tcgen05_sink(const void*, const void*, const void*, const int*, const int*, const int*,
+                                       const int*, const int*, int, int, int, void*, int, int, int, int, int, int,
+                                       float, const float*, cudaStream_t);
+int fwb_attention_decode_mma_sink(const void*, const void*, const void*, const int*, const int*, const int*, int,
+                                  int, int, void*, float*, float*, int, int, int, int, int, int, int, float, int,
+                                  const float*, int, cudaStream_t);
+int fwb_embed_pair_hash(const void*, const void*, int, const int*, const int*, const int*, const int*, const int*,
+                        int*, long long, float*, int, int, int, int, long long, long long, int*, float,
+                        cudaStream_t);
+int fwb_token_shift(const float*, const float*, float*, long long, const int*, const int*, const int*, const int*,
+                    void*, int, int, int, cudaStream_t);
+int fwb_unit_rms_gain_add(float*, const float*, const float*, void*, int, int, int, float, cudaStream_t);
+int fwb_latent_prepare(const void*, int, int, int, const float*, const float*, const int*, const int*, const int*,
+                       int, int, void*, void*, int, int, int, int, int, int, int, int, int, float, cudaStream_t);
+int fwb_head_linear(const void*, const void*, void*, int, int, int, int, int, long long, long long, long long,
+                    long long, cudaStream_t);
+int fwb_head_linear_mma(const void*, const void*, void*, int, int, int, int, long long, long long, long long,
+                        long long, cudaStream_t);
+int fwb_latent_attention_simt(const void*, const void*, int, const float*, const int*, const int*, const int*, int,
+                              int, void*, int, int, int, int, int, float, cudaStream_t);
 }
 
 namespace {
@@ -72,9 +95,10 @@ enum Option {
     OPT_FORCE_TILED = 8,       // single decode tokens through the tiled attention kernel
     OPT_ATTENTION_TCGEN05 = 9, // prompt portions through the tcgen05 attention kernel
     OPT_MIXED_SPLIT = 10,      // decoding requests at the head of a mixed step through the decode kernel
-    OPT_COUNT = 11,
+    OPT_LATENT_TENSORCORE = 11, // latent attention and its per-head products on tensor cores
+    OPT_COUNT = 12,
 };
-int g_option[OPT_COUNT] = {1, 0, 1, 1, 1, 1, 0, 1, 0, 1, 1};
+int g_option[OPT_COUNT] = {1, 0, 1, 1, 1, 1, 0, 1, 0, 1, 1, 1};
 constexpr int FUSE_FROM_TOKENS = 16;
 constexpr int CLUSTER_MERGE_CTAS = 1024;
 
@@ -273,7 +297,9 @@ void linear(Launches& L, const void* x, int x_bf16, const void* w, int w_bf16, v
 }
 
 // ---- operations of a plan -----------------------------------------------------------------
-enum OpKind { OP_EMBED, OP_NORM_LINEAR, OP_LINEAR_RESIDUAL, OP_SHORTCONV, OP_QK_ROPE, OP_ATTENTION, OP_SOFTCAP };
+enum OpKind { OP_EMBED, OP_NORM_LINEAR, OP_LINEAR_RESIDUAL, OP_SHORTCONV, OP_QK_ROPE, OP_ATTENTION, OP_SOFTCAP,
+              OP_EMBED_PAIRS, OP_TOKEN_SHIFT, OP_LINEAR, OP_SWIGLU, OP_LATENT_PREPARE, OP_HEAD_LINEAR,
+              OP_LATENT_ATTENTION, OP_GAIN_ADD };
 // ids of the step's int32 arrays (their offsets into the uploaded block come with every step)
 enum MetaArray { META_TOKEN_IDS, META_POSITIONS, META_TOK_SEG, META_SEG_START, META_SEG_SLOT, META_SEG_POS0,
                  META_LOGIT_ROWS, META_TILE_SEG_A, META_TILE_TOK0_A, META_TILE_SEG_B, META_TILE_TOK0_B,
@@ -305,6 +331,17 @@ struct Op {
     int page_size = 0, num_pages = 0, vocab = 0;
     long long stride = 0;
     float eps = 0.0f, scale = 1.0f;
+    // attention: a score per head in the softmax denominator; heads the pools have (0: nkv; fewer than
+    // nkv: nkv counts groups of query heads that share a pool head)
+    const float* sink = nullptr;
+    int pool_nkv = 0;
+    // latent attention: latent entries, entries that enter a score, entries of a cache row, plain query
+    // channels per head, column of the latent projection in its row, that row's length
+    int rank = 0, used = 0, row = 0, dim = 0, kv_col = 0, ld = 0;
+    // per-head products: heads, row lengths and head offsets of input and output
+    int heads = 0;
+    long long ldx = 0, x_head = 0, ldy = 0, y_head = 0;
+    long long mul_prev = 0, mul_cur = 0;   // hashed pair embedding
 };
 
 constexpr int STAGING = 4;
@@ -460,10 +497,11 @@ void run_decode_attention(Launches& L, const Op& op, const FwbStep& step, const 
     decode_splits(n_tokens, op.nkv, width, op.hd, splits, tiles_per_split, in_cluster);
     const bool merged_in_kernel = in_cluster && splits > 1 && splits <= 8;
     const bool scratch = splits > 1 && !merged_in_kernel;
-    L.add(fwb_attention_decode_mma(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS), meta(step, META_TOK_SEG),
-                                   table, width, op.page_size, op.num_pages, op.out, scratch ? op.part_o : nullptr,
-                                   scratch ? op.part_ml : nullptr, n_tokens, op.nh, op.nkv, op.hd, splits,
-                                   tiles_per_split, op.window, op.scale, merged_in_kernel ? 1 : 0, stream),
+    L.add(fwb_attention_decode_mma_sink(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS),
+                                        meta(step, META_TOK_SEG), table, width, op.page_size, op.num_pages, op.out,
+                                        scratch ? op.part_o : nullptr, scratch ? op.part_ml : nullptr, n_tokens,
+                                        op.nh, op.nkv, op.hd, splits, tiles_per_split, op.window, op.scale,
+                                        merged_in_kernel ? 1 : 0, op.sink, op.pool_nkv, stream),
           scratch ? 2 : 1);
 }
 
@@ -485,28 +523,80 @@ void run_attention(Launches& L, const Op& op, const FwbStep& step, int act_bf16,
             first = step.leading_singles;
             run_decode_attention(L, op, step, table, width, first, stream);
         }
+        // the tcgen05 kernel takes up to 128 query heads per pool head in one tile: no cut into groups
+        const int pool_heads = op.pool_nkv > 0 ? op.pool_nkv : op.nkv;
+        const int wide = op.nh / pool_heads;
         const bool tcgen05_shape = (op.hd == 64 || op.hd == 128) && op.page_size == 64 && op.nkv > 0 &&
-                                   op.nh % op.nkv == 0 && group <= 128;
+                                   op.nh % pool_heads == 0 && wide <= 128;
         // tile list A holds 128-row tiles, list B 64-row tiles; both skip the leading singles
         // exactly when the decode kernel took them
-        if (g_option[OPT_ATTENTION_TCGEN05] && !force_tiled && tcgen05_shape && 2 * step.max_segment * group >= 128) {
-            L.add(fwb_attention_prefill_tcgen05(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS),
-                                                meta(step, META_SEG_START), meta(step, META_TILE_SEG_A),
-                                                meta(step, META_TILE_TOK0_A), table, width, op.page_size,
-                                                op.num_pages, op.out, step.n_tiles[0], op.nh, op.nkv, op.hd,
-                                                step.tokens_per_tile[0], op.window, op.scale, stream));
+        if (g_option[OPT_ATTENTION_TCGEN05] && !force_tiled && tcgen05_shape && 2 * step.max_segment * wide >= 128) {
+            L.add(fwb_attention_prefill_tcgen05_sink(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS),
+                                                     meta(step, META_SEG_START), meta(step, META_TILE_SEG_A),
+                                                     meta(step, META_TILE_TOK0_A), table, width, op.page_size,
+                                                     op.num_pages, op.out, step.n_tiles[0], op.nh, pool_heads,
+                                                     op.hd, step.tokens_per_tile[0], op.window, op.scale, op.sink,
+                                                     stream));
             return;
         }
-        L.add(fwb_attention_prefill_mma(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS),
-                                        meta(step, META_SEG_START), meta(step, META_TILE_SEG_B),
-                                        meta(step, META_TILE_TOK0_B), table, width, op.page_size, op.out,
-                                        step.n_tiles[1], op.nh, op.nkv, op.hd, step.tokens_per_tile[1], op.window,
-                                        op.scale, stream));
+        L.add(fwb_attention_prefill_mma_sink(op.in, op.pool_k, op.pool_v, meta(step, META_POSITIONS),
+                                             meta(step, META_SEG_START), meta(step, META_TILE_SEG_B),
+                                             meta(step, META_TILE_TOK0_B), table, width, op.page_size, op.out,
+                                             step.n_tiles[1], op.nh, op.nkv, op.hd, step.tokens_per_tile[1],
+                                             op.window, op.scale, op.sink, op.pool_nkv, stream));
+        return;
+    }
+    if (op.kind == OP_LATENT_ATTENTION) {
+        L.add(FWB_UNSUPPORTED, 0);       // the caller runs the fp32 kernel of the latent form instead
         return;
     }
     L.add(fwb_attention_simt(op.in, act_bf16, op.pool_k, op.pool_v, act_bf16, meta(step, META_POSITIONS),
                              meta(step, META_TOK_SEG), table, width, op.page_size, op.out, act_bf16, T, op.nh,
                              op.nkv, op.hd, op.window, op.scale, stream));
+}
+
+// gate|up with silu(g)*u from activations that are already there (no norm in front).
+void run_swiglu(Launches& L, const Op& op, const FwbStep& step, int act_bf16, cudaStream_t stream) {
+    const int M = step.T;
+    if (op.w_bf16 && act_bf16 && tc_accepts(op.in, op.w, M, op.K)) {
+        tc_swiglu(L, op.in, op.w, op.out, M, op.N, op.K, stream);
+        return;
+    }
+    linear(L, op.in, act_bf16, op.w, op.w_bf16, op.scratch2, act_bf16, nullptr, M, 2 * op.N, op.K, stream);
+    L.add(fwb_silu_mul(op.scratch2, act_bf16, op.out, act_bf16, M, op.N, stream));
+}
+
+// Y[t][h] = W[h] X[t][h] for every head: tensor cores when everything is bfloat16 and even.
+void run_head_linear(Launches& L, const void* in, const void* w, void* out, int M, int N, int K, int heads,
+                     long long ldx, long long x_head, long long ldy, long long y_head, int act_bf16,
+                     cudaStream_t stream) {
+    const bool even = ((N | K | ldx | x_head | ldy | y_head) & 1) == 0;
+    if (g_option[OPT_LATENT_TENSORCORE] && act_bf16 && even)
+        L.add(fwb_head_linear_mma(in, w, out, M, N, K, heads, ldx, x_head, ldy, y_head, stream));
+    else
+        L.add(fwb_head_linear(in, w, out, act_bf16, M, N, K, heads, ldx, x_head, ldy, y_head, stream));
+}
+
+// Attention of the query rows [T][heads][row] over the cached latent rows, then the per-head value
+// product on the weighted rows' first `rank` entries: bfloat16 on the paged tensor-core kernels (one
+// pool head for all query heads, rows as keys and values), else the fp32 kernel of the latent form.
+void run_latent_attention(Launches& L, const Op& op, const FwbStep& step, int act_bf16, cudaStream_t stream) {
+    const int T = step.T;
+    const bool mma_shape = op.nkv > 0 && op.nh % op.nkv == 0 && op.nh / op.nkv <= 16 && op.row >= 16 &&
+                           op.row <= 128 && op.row % 16 == 0 && op.page_size == 64;
+    long long stride = op.rank;
+    if (g_option[OPT_LATENT_TENSORCORE] && g_option[OPT_ATTENTION_MMA] && act_bf16 && mma_shape) {
+        run_attention(L, op, step, act_bf16, stream);
+        stride = op.row;
+    } else {
+        L.add(fwb_latent_attention_simt(op.in, op.pool_k, act_bf16, op.sink, meta(step, META_POSITIONS),
+                                        meta(step, META_TOK_SEG), meta(step, META_BLOCK_TABLE0 + op.group),
+                                        step.width[op.group], op.page_size, op.out, T, op.nh, op.rank, op.used,
+                                        op.row, op.scale, stream));
+    }
+    if (!L.ok()) return;
+    run_head_linear(L, op.out, op.w, op.scratch, T, op.N, op.rank, op.nh, (long long)op.nh * stride, stride,
+                    op.ldy, op.y_head, act_bf16, stream);
 }
 
 }  // namespace
@@ -679,6 +769,189 @@ FWB_API int fwb_plan_attention(void* handle, const void* q, void* k_pool, void* 
     return FWB_OK;
 }
 
+// x[T][H] = scale * table[id] + pairs[(id_before * mul_prev + id * mul_cur) mod buckets] (row `buckets` at
+// position 0); last_token: one int32 per state slot, `slot_stride` words apart.
+FWB_API int fwb_plan_embed_pairs(void* handle, const void* table, const void* pairs, int tables_bf16, float* x,
+                                 int H, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                                 float scale, int* last_token, long long slot_stride, int* bad_flag) {
+    if (!handle || !table || !pairs || !x || !last_token || buckets <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_EMBED_PAIRS;
+    op.table = table;
+    op.w = pairs;
+    op.w_bf16 = tables_bf16;
+    op.x = x;
+    op.K = H;
+    op.vocab = vocab;
+    op.N = buckets;
+    op.mul_prev = mul_prev;
+    op.mul_cur = mul_cur;
+    op.scale = scale;
+    op.pool_k = last_token;
+    op.stride = slot_stride;
+    op.flag = bad_flag;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// out[t] = x[t] + (x[t-1] - x[t]) * mu along every request's tokens, in the activation dtype;
+// state: every slot's last row of x (fp32), `slot_stride` floats apart.
+FWB_API int fwb_plan_token_shift(void* handle, float* x, const float* mu, float* state, long long slot_stride,
+                                 void* out, int W) {
+    if (!handle || !x || !mu || !state || !out || W <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_TOKEN_SHIFT;
+    op.x = x;
+    op.v0 = mu;
+    op.pool_k = state;
+    op.stride = slot_stride;
+    op.out = out;
+    op.K = W;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// out = in @ w^T for activations that are already there; out_f32: fp32 [.][N], else the activation dtype.
+FWB_API int fwb_plan_linear(void* handle, const void* in, const void* w, int w_bf16, int N, int K, void* out,
+                            int out_f32) {
+    if (!handle || !in || !w || !out || N <= 0 || K <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_LINEAR;
+    op.in = const_cast<void*>(in);
+    op.w = w;
+    op.w_bf16 = w_bf16;
+    op.N = N;
+    op.K = K;
+    op.out = out;
+    op.epilogue = out_f32 ? EPI_F32 : EPI_BF16;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// out[.][F] = silu(in @ gate^T) * (in @ up^T), w = [gate | up] ([2F][K]); scratch2: [tokens][2F] activations.
+FWB_API int fwb_plan_swiglu(void* handle, const void* in, const void* w, int w_bf16, int F, int K, void* out,
+                            void* scratch2) {
+    if (!handle || !in || !w || !out || !scratch2 || F <= 0 || K <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_SWIGLU;
+    op.in = const_cast<void*>(in);
+    op.w = w;
+    op.w_bf16 = w_bf16;
+    op.N = F;
+    op.K = K;
+    op.out = out;
+    op.scratch2 = scratch2;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// The rotated part of every query head into qa [T][heads][row] (columns rank..row), and, with a pool, the
+// token's cache row (normed latent, turned key part, padding).  proj: [T][ld], queries at column 0, the
+// latent projection at column kv_col.
+FWB_API int fwb_plan_latent_prepare(void* handle, const void* proj, int ld, int kv_col, const float* norm_w,
+                                    const void* table, void* qa, void* pool, int group, int page_size, int heads,
+                                    int dim, int rot, int rot_dims, int pairing, int rank, int row, float eps) {
+    if (!handle || !proj || !table || !qa || group < 0 || group >= MAX_GROUPS) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_LATENT_PREPARE;
+    op.in = const_cast<void*>(proj);
+    op.ld = ld;
+    op.kv_col = kv_col;
+    op.v0 = norm_w;
+    op.table = table;
+    op.out = qa;
+    op.pool_k = pool;
+    op.group = group;
+    op.page_size = page_size;
+    op.nh = heads;
+    op.dim = dim;
+    op.hd = rot;
+    op.rot = rot_dims;
+    op.pairing = pairing;
+    op.rank = rank;
+    op.row = row;
+    op.eps = eps;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// out[t][h*y_head + n] = sum_k w[h][n][k] * in[t][h*x_head + k]; w: [heads][N][K].
+FWB_API int fwb_plan_head_linear(void* handle, const void* in, const void* w, void* out, int N, int K, int heads,
+                                 long long ldx, long long x_head, long long ldy, long long y_head) {
+    if (!handle || !in || !w || !out || N <= 0 || K <= 0 || heads <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_HEAD_LINEAR;
+    op.in = const_cast<void*>(in);
+    op.w = w;
+    op.out = out;
+    op.N = N;
+    op.K = K;
+    op.heads = heads;
+    op.ldx = ldx;
+    op.x_head = x_head;
+    op.ldy = ldy;
+    op.y_head = y_head;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// Attention of qa [T][heads][row] over the latent pool [pages][1][page_size][row] (`groups`: the query
+// heads in groups of at most 16 that all read the one pool head), with a sink per head or none; `mixed`
+// [T][heads][row] receives the weighted rows; then heads_out[t][h*vdim + n] = sum_k w_uv[h][n][k] *
+// mixed[t][h][k], k < rank.
+FWB_API int fwb_plan_latent_attention(void* handle, const void* qa, void* pool, const float* sink, void* mixed,
+                                      const void* w_uv, void* heads_out, int group, int page_size, int num_pages,
+                                      int heads, int groups, int rank, int used, int row, int vdim, float scale,
+                                      float* part_o, float* part_ml) {
+    if (!handle || !qa || !pool || !mixed || !w_uv || !heads_out || group < 0 || group >= MAX_GROUPS)
+        return FWB_BAD_ARGUMENT;
+    if (heads <= 0 || groups <= 0 || heads % groups || rank <= 0 || used < rank || row < used || vdim <= 0)
+        return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_LATENT_ATTENTION;
+    op.in = const_cast<void*>(qa);
+    op.pool_k = pool;
+    op.pool_v = pool;
+    op.sink = sink;
+    op.out = mixed;
+    op.w = w_uv;
+    op.scratch = heads_out;
+    op.group = group;
+    op.page_size = page_size;
+    op.num_pages = num_pages;
+    op.nh = heads;
+    op.nkv = groups;
+    op.pool_nkv = 1;
+    op.hd = row;
+    op.rank = rank;
+    op.used = used;
+    op.row = row;
+    op.N = vdim;
+    op.ldy = (long long)heads * vdim;
+    op.y_head = vdim;
+    op.scale = scale;
+    op.part_o = part_o;
+    op.part_ml = part_ml;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
+// x += gain * y / sqrt(mean(y^2) + eps) row by row; copy (may be null): the new x in the activation dtype.
+FWB_API int fwb_plan_gain_add(void* handle, float* x, const float* y, const float* gain, float eps, void* copy,
+                              int W) {
+    if (!handle || !x || !y || !gain || W <= 0) return FWB_BAD_ARGUMENT;
+    Op op;
+    op.kind = OP_GAIN_ADD;
+    op.x = x;
+    op.in = const_cast<float*>(y);
+    op.v0 = gain;
+    op.eps = eps;
+    op.out = copy;
+    op.K = W;
+    static_cast<Plan*>(handle)->ops.push_back(op);
+    return FWB_OK;
+}
+
 FWB_API int fwb_plan_softcap(void* handle, float cap, int vocab) {
     if (!handle || !(cap > 0.0f)) return FWB_BAD_ARGUMENT;
     Op op;
@@ -744,6 +1017,44 @@ FWB_API int fwb_plan_run(void* handle, const void* step_ptr, int* launches, cuda
                 break;
             case OP_ATTENTION:
                 run_attention(L, op, step, act_bf16, stream);
+                break;
+            case OP_EMBED_PAIRS:
+                L.add(fwb_embed_pair_hash(op.table, op.w, op.w_bf16, meta(step, META_TOKEN_IDS),
+                                          meta(step, META_POSITIONS), meta(step, META_TOK_SEG),
+                                          meta(step, META_SEG_START), meta(step, META_SEG_SLOT), (int*)op.pool_k,
+                                          op.stride, op.x, step.T, op.K, op.vocab, op.N, op.mul_prev, op.mul_cur,
+                                          op.flag, op.scale, stream));
+                break;
+            case OP_TOKEN_SHIFT:
+                L.add(fwb_token_shift(op.x, op.v0, (float*)op.pool_k, op.stride, meta(step, META_POSITIONS),
+                                      meta(step, META_TOK_SEG), meta(step, META_SEG_START),
+                                      meta(step, META_SEG_SLOT), op.out, act_bf16, step.T, op.K, stream));
+                break;
+            case OP_LINEAR:
+                linear(L, op.in, act_bf16, op.w, op.w_bf16, op.out, op.epilogue == EPI_BF16 ? act_bf16 : 0, nullptr,
+                       step.T, op.N, op.K, stream);
+                break;
+            case OP_SWIGLU:
+                run_swiglu(L, op, step, act_bf16, stream);
+                break;
+            case OP_LATENT_PREPARE:
+                L.add(fwb_latent_prepare(op.in, act_bf16, op.ld, op.kv_col, op.v0, (const float*)op.table,
+                                         meta(step, META_POSITIONS), meta(step, META_TOK_SEG),
+                                         op.pool_k ? meta(step, META_BLOCK_TABLE0 + op.group) : nullptr,
+                                         op.pool_k ? step.width[op.group] : 0, op.pool_k ? op.page_size : 0, op.out,
+                                         op.pool_k, act_bf16, step.T, op.nh, op.dim, op.hd, op.rot, op.pairing,
+                                         op.rank, op.row, op.eps, stream));
+                break;
+            case OP_HEAD_LINEAR:
+                run_head_linear(L, op.in, op.w, op.out, step.T, op.N, op.K, op.heads, op.ldx, op.x_head, op.ldy,
+                                op.y_head, act_bf16, stream);
+                break;
+            case OP_LATENT_ATTENTION:
+                run_latent_attention(L, op, step, act_bf16, stream);
+                break;
+            case OP_GAIN_ADD:
+                L.add(fwb_unit_rms_gain_add(op.x, (const float*)op.in, op.v0, op.out, act_bf16, step.T, op.K,
+                                            op.eps, stream));
                 break;
             case OP_SOFTCAP:
                 if (step.R > 0)

@@ -117,7 +117,7 @@ class PlanBuilder:
         self._arena = _Arena()
         self._ops = []                      # (launcher name, argument tuple with Buf placeholders)
         self._keep = []                     # tensors the plan's pointers refer to
-        self.group_sizes = set()            # query heads per KV head of the attention operations
+        self.tile_tokens = set()            # (tokens per 128-row tile, per 64-row tile) of the attention operations
         self.x = self.tokens(hidden, torch.float32)
         self.delta = self.tokens(hidden, torch.float32)
 
@@ -226,7 +226,7 @@ class PlanBuilder:
         num_pages, n_kv, page_size, head_dim = k_pool.shape
         if k_pool.dtype != self.act_dtype:
             raise NotPlannable("the cache is not in the activation dtype")
-        self.group_sizes.add(n_heads // n_kv)
+        self.tile_tokens.add((max(1, 128 // (n_heads // n_kv)), max(1, 64 // (n_heads // n_kv))))
         # scratch of the split decode kernel when its slices are merged by a second kernel: only
         # single tokens go there, one per live request at most, in at most 16 slices
         part_o = self.sized(self.num_slots * n_kv * 16 * (n_heads // n_kv) * head_dim * 4)
@@ -236,6 +236,102 @@ class PlanBuilder:
                            head_dim, int(window), ctypes.c_float(scale), part_o, part_ml)))
         self.free(part_o)
         self.free(part_ml)
+
+    # ---- operations of models whose sublayers read the stream itself (no norm in front of a product)
+    def _state(self, state: torch.Tensor, row: int, dtype, what: str) -> int:
+        if state is None or state.dtype != dtype or state.dim() != 2 or state.shape[1] != row \
+                or (row > 1 and state.stride(1) != 1):
+            raise NotPlannable(f"{what} is not {dtype} [slots][{row}] with contiguous rows")
+        self._keep.append(state)
+        return state.stride(0) if state.shape[0] > 1 else max(row, 1)
+
+    def embed_pairs(self, table: torch.Tensor, pairs: torch.Tensor, vocab: int, buckets: int, mul_prev: int,
+                    mul_cur: int, scale: float, last_token: torch.Tensor) -> None:
+        """``x = scale * table[id] + pairs[hash(id before, id)]``; ``last_token``: int32 [slots][1]."""
+        if not table.is_contiguous() or not pairs.is_contiguous() or pairs.dtype != table.dtype:
+            raise NotPlannable("the embedding tables are not contiguous tensors of one dtype")
+        self._keep += [table, pairs]
+        stride = self._state(last_token, 1, torch.int32, "the last-token state")
+        self._ops.append(("fwb_plan_embed_pairs",
+                          (table, pairs, kernel_lib.is_bf16(table), self.x, self.hidden, int(vocab), int(buckets),
+                           ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), ctypes.c_float(scale),
+                           last_token, ctypes.c_longlong(stride), self.bad_flag)))
+
+    def token_shift(self, mu: torch.Tensor, state: torch.Tensor, out: Buf) -> None:
+        """``out[t] = x[t] + (x[t-1] - x[t]) * mu`` in the activation dtype; ``state``: fp32 [slots][H]."""
+        stride = self._state(state, self.hidden, torch.float32, "the shift state")
+        self._ops.append(("fwb_plan_token_shift", (self.x, self._vector(mu), state, ctypes.c_longlong(stride), out,
+                                                   self.hidden)))
+
+    def linear(self, inp, w: torch.Tensor, out: Buf, what: str) -> None:
+        """``out = inp @ w.T`` from activations that are already there (``inp``: a buffer in the activation
+        dtype); ``out`` in fp32 or in the activation dtype, as the buffer says."""
+        w_bf16 = self.matrix(w, what)
+        if w.shape[1] != inp.width or w.shape[0] != out.width:
+            raise NotPlannable(f"{what}: shape {tuple(w.shape)} does not map {inp.width} to {out.width}")
+        self._ops.append(("fwb_plan_linear", (inp, w, w_bf16, w.shape[0], w.shape[1], out,
+                                              1 if out.dtype == torch.float32 else 0)))
+
+    def swiglu(self, inp, w_gate_up: torch.Tensor, out: Buf, what: str) -> None:
+        """``out = silu(inp @ gate.T) * (inp @ up.T)`` for ``w_gate_up`` = [gate | up]."""
+        w_bf16 = self.matrix(w_gate_up, what)
+        F, K = w_gate_up.shape[0] // 2, w_gate_up.shape[1]
+        if K != inp.width or F != out.width:
+            raise NotPlannable(f"{what}: shape {tuple(w_gate_up.shape)} does not map {inp.width} to 2 x {out.width}")
+        scratch2 = self.tokens(2 * F, self.act_dtype)
+        self._ops.append(("fwb_plan_swiglu", (inp, w_gate_up, w_bf16, F, K, out, scratch2)))
+        self.free(scratch2)
+
+    def latent_prepare(self, proj: Buf, kv_col: int, norm_w, table: torch.Tensor, qa: Buf, cache, writes: bool,
+                       heads: int, dim: int, rot: int, rot_dims: int, pairing: str, rank: int, row: int,
+                       eps: float) -> None:
+        self._keep.append(table)
+        pool = cache.k_pool if writes else None
+        if writes and pool.dtype != self.precision.cache_dtype:
+            raise NotPlannable("the latent pool is not in the cache dtype")
+        if self.precision.cache_dtype != self.act_dtype:
+            raise NotPlannable("the cache is not in the activation dtype")
+        self._ops.append(("fwb_plan_latent_prepare",
+                          (proj, proj.width, int(kv_col), self._vector(norm_w) if writes else None, table, qa, pool,
+                           self._group(cache), pool.shape[2] if writes else 0, heads, dim, rot, rot_dims,
+                           ROPE_PAIRINGS[pairing], rank, row, ctypes.c_float(eps))))
+
+    def head_linear(self, inp: Buf, x_head: int, w: torch.Tensor, out: Buf, y_head: int, what: str) -> None:
+        """``out[t][h*y_head + n] = sum_k w[h][n][k] * inp[t][h*x_head + k]`` for w [heads][N][K]."""
+        self.matrix(w, what)
+        heads, N, K = w.shape
+        if (heads - 1) * x_head + K > inp.width or (heads - 1) * y_head + N > out.width:
+            raise NotPlannable(f"{what}: a head lies outside its row")
+        self._ops.append(("fwb_plan_head_linear", (inp, w, out, N, K, heads, ctypes.c_longlong(inp.width),
+                                                   ctypes.c_longlong(x_head), ctypes.c_longlong(out.width),
+                                                   ctypes.c_longlong(y_head))))
+
+    def latent_attention(self, qa: Buf, cache, sink, w_uv: torch.Tensor, heads_out: Buf, heads: int, rank: int,
+                         used: int, row: int, scale: float) -> None:
+        """Attention of the query rows over the cached latent rows and the per-head value product."""
+        pool = cache.k_pool
+        num_pages, pool_heads, page_size, width = pool.shape
+        if pool_heads != 1 or width != row or pool.dtype != self.act_dtype:
+            raise NotPlannable("the latent pool is not [pages][1][page][row] in the activation dtype")
+        self.matrix(w_uv, "the per-head value product")
+        groups = attention_kernels.head_groups(heads, 1) or 1
+        self.tile_tokens.add((max(1, 128 // heads), max(1, 64 // (heads // groups))))
+        mixed = self.tokens(heads * row, self.act_dtype)
+        # scratch of the split decode kernel: one pool head for every token, so a lone request is cut into
+        # as many slices as the kernel's rule allows (64)
+        part_o = self.sized(self.num_slots * heads * 64 * row * 4)
+        part_ml = self.sized(self.num_slots * heads * 64 * 2 * 4)
+        self._ops.append(("fwb_plan_latent_attention",
+                          (qa, pool, self._vector(sink), mixed, w_uv, heads_out, self._group(cache), page_size,
+                           num_pages, heads, groups, rank, used, row, w_uv.shape[1], ctypes.c_float(scale),
+                           part_o, part_ml)))
+        for buf in (mixed, part_o, part_ml):
+            self.free(buf)
+
+    def gain_add(self, y: Buf, gain: torch.Tensor, eps: float, copy: Optional[Buf]) -> None:
+        """``x += gain * y / sqrt(mean(y^2) + eps)``; ``copy``: the new x in the activation dtype as well."""
+        self._ops.append(("fwb_plan_gain_add", (self.x, y, self._vector(gain), ctypes.c_float(eps), copy,
+                                                self.hidden)))
 
     def softcap(self, cap: float, vocab: int) -> None:
         self._ops.append(("fwb_plan_softcap", (ctypes.c_float(cap), int(vocab))))
@@ -248,8 +344,8 @@ class PlanBuilder:
 
     # ------------------------------------------------------------------ the finished plan
     def finish(self, n_groups: int, vocab: int) -> "StepPlan":
-        if len(self.group_sizes) > 1:
-            raise NotPlannable("attention layers with different numbers of query heads per KV head")
+        if len(self.tile_tokens) > 1:
+            raise NotPlannable("attention layers whose query heads fill the kernels' row tiles differently")
         arena = torch.empty(max(self._arena.top, 256), dtype=torch.uint8, device=self.device)
         base = arena.data_ptr()
         library = kernel_lib.library()
@@ -270,22 +366,22 @@ class PlanBuilder:
             if status != 0:
                 library.fwb_plan_destroy(handle)
                 raise KernelError(f"{name} refused its arguments while the plan was built (status {status})")
-        group = next(iter(self.group_sizes), 1)
-        return StepPlan(handle, arena, self._keep, self.device, n_groups, vocab, group, self.max_tokens,
+        tile_tokens = next(iter(self.tile_tokens), (128, 64))
+        return StepPlan(handle, arena, self._keep, self.device, n_groups, vocab, tile_tokens, self.max_tokens,
                         self.max_rows, len(self._ops))
 
 
 class StepPlan:
     """A built plan.  ``run`` executes one step: segments in, fp32 logits [wanted][vocab] out."""
 
-    def __init__(self, handle, arena, keep, device, n_groups, vocab, group, max_tokens, max_rows, n_ops):
+    def __init__(self, handle, arena, keep, device, n_groups, vocab, tile_tokens, max_tokens, max_rows, n_ops):
         self._handle = handle
         self._arena = arena
         self._keep = keep
         self.device = device
         self.n_groups = n_groups
         self.vocab = vocab
-        self.tokens_per_tile = (max(1, 128 // group), max(1, 64 // group))
+        self.tokens_per_tile = tuple(tile_tokens)
         self.max_tokens, self.max_rows = max_tokens, max_rows
         self.n_ops = n_ops
         self._library = kernel_lib.library()
@@ -442,16 +538,26 @@ def build_plan(model, caches, max_tokens: int, max_rows: int, num_slots: int, n_
     builder = PlanBuilder(model.precision, model.device, spec.hidden_size, max_tokens, max_rows, num_slots,
                           bad_flag)
     try:
-        if getattr(model, "embedder", None) is not None:
-            raise NotPlannable(f"embedding {model.embedder.kind!r} has no native form")
-        builder.embed(model.embedding, spec.vocab_size, spec.embedding_scale)
+        embedder = getattr(model, "embedder", None)
+        if embedder is None:
+            builder.embed(model.embedding, spec.vocab_size, spec.embedding_scale)
+        elif getattr(embedder, "plan", None) is None:
+            raise NotPlannable(f"embedding {embedder.kind!r} has no native form")
+        else:
+            own = len(spec.schedule)
+            embedder.plan(builder, model.embedding, spec.vocab_size, caches[own] if len(caches) > own else None)
         for position, entry in enumerate(spec.schedule):
             source = position if entry.cache_of is None else entry.cache_of
             layer = model.layers[entry.layer]
             plan = getattr(layer, "plan", None)
             if plan is None:
                 raise NotPlannable(f"arrangement {layer.layer.arrangement!r} has no native form")
-            plan(builder, caches[source])
+            # a position that reads another's pages finds them in its own entry when the manager was
+            # told so (beside the fixed-size state that is its own); else the source's entry serves
+            own_entry = caches[position]
+            shared = entry.cache_of is not None and getattr(own_entry, "k_pool", None) is None \
+                and getattr(own_entry, "state", None) is None
+            plan(builder, caches[source] if shared else own_entry)
         builder.norm_linear(model.final_norm, model.head, EPI_F32, None, "the head", on_logit_rows=True)
         if spec.logit_softcap > 0:
             builder.softcap(spec.logit_softcap, spec.vocab_size)

@@ -24,6 +24,10 @@ def set_mma_enabled(flag: bool) -> None:
     lib.set_option("attention_mma", _use_mma)
 
 
+def mma_enabled() -> bool:
+    return _use_mma
+
+
 _force_tiled = False
 _use_tcgen05 = True
 

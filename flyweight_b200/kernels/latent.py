@@ -108,10 +108,12 @@ def set_tensor_cores(flag: bool) -> None:
     (on by default) or the fp32-FMA kernels for everything."""
     global _mma_enabled
     _mma_enabled = bool(flag)
+    lib.set_option("latent_tensorcore", _mma_enabled)
 
 
 def tensor_cores() -> bool:
-    return _mma_enabled
+    from . import attention
+    return _mma_enabled and attention.mma_enabled()
 
 
 def head_linear(x: torch.Tensor, x_col: int, x_head: int, in_features: int, w: torch.Tensor,

@@ -203,7 +203,7 @@ def call(name: str, *args, launches: int = 1, tag: Optional[str] = None) -> None
 # kernels/tensorcore.py and kernels/attention.py keep both sides equal.
 OPTIONS = {"tensorcore": 0, "forced_splits": 1, "pairs": 2, "mid_size_split": 3, "fuse_norm": 4,
            "add_in_place": 5, "fuse_always": 6, "attention_mma": 7, "force_tiled": 8,
-           "attention_tcgen05": 9, "mixed_split": 10}
+           "attention_tcgen05": 9, "mixed_split": 10, "latent_tensorcore": 11}
 
 
 def set_option(name: str, value: int) -> None:

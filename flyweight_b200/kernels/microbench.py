@@ -86,21 +86,35 @@ def _paged_inputs(batch, context, new, n_heads, n_kv, head_dim):
     return q, k_pool, v_pool, table.cuda(), width
 
 
+def _shared_rows(args, k_pool):
+    """``--shared-rows``: the form latent attention uses -- one pool head that every query head reads
+    (in groups of at most 16), its rows keys and values at once, and a sink per head."""
+    from . import attention
+    groups = attention.head_groups(args.heads, 1)
+    sink = torch.randn(args.heads, device="cuda", dtype=torch.float32)
+    return k_pool, {"sink": sink, "groups": groups}, groups
+
+
 def run_attention_decode(args) -> dict:
     from . import attention, ops
     B, ctx = args.batch, args.context
+    if args.shared_rows:
+        args.kv_heads = 1
     q, k_pool, v_pool, table, width = _paged_inputs(B, ctx, 1, args.heads, args.kv_heads, args.head_dim)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
     tok_seg = torch.arange(B, dtype=torch.int32, device="cuda")
-    splits, per, in_cluster = attention.decode_splits(B, args.kv_heads, width, args.head_dim)
+    extra, groups = {}, args.kv_heads
+    if args.shared_rows:
+        v_pool, extra, groups = _shared_rows(args, k_pool)
+    splits, per, in_cluster = attention.decode_splits(B, groups, width, args.head_dim)
     if args.splits:
         splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
     ops.set_decode_attention_tma(not args.cp_async, args.stages)
     us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
-                                                args.heads, 0, scale, splits, per, in_cluster), args.repeat)
+                                                args.heads, 0, scale, splits, per, in_cluster, **extra), args.repeat)
     ops.set_decode_attention_tma(True)
-    kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * 2
+    kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * (1 if args.shared_rows else 2)
     from . import tensorcore
     return {"kernel": "attention_decode_mma", "batch": B, "context": ctx, "splits": splits,
             "tiles_by": "cp.async" if args.cp_async or args.head_dim not in (64, 128) else "tma",
@@ -110,8 +124,17 @@ def run_attention_decode(args) -> dict:
 def run_attention_prefill(args) -> dict:
     from . import ops
     T = args.tokens
+    if args.shared_rows:
+        args.kv_heads = 1
     group = args.heads // args.kv_heads
     q, k_pool, v_pool, table, _ = _paged_inputs(1, T, T, args.heads, args.kv_heads, args.head_dim)
+    extra = {}
+    if args.shared_rows:
+        v_pool, extra, groups = _shared_rows(args, k_pool)
+        if args.mma_sync:
+            group = args.heads // groups
+        else:
+            extra.pop("groups")
     positions = torch.arange(T, dtype=torch.int32, device="cuda")
     seg_start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
     per_tile = max(1, (64 if args.mma_sync else 128) // group)
@@ -121,7 +144,7 @@ def run_attention_prefill(args) -> dict:
     scale = 1.0 / math.sqrt(args.head_dim)
     kernel = ops.attention_prefill_mma if args.mma_sync else ops.attention_prefill_tcgen05
     us = _time(lambda: kernel(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
-                              per_tile, table, args.heads, 0, scale), args.repeat)
+                              per_tile, table, args.heads, 0, scale, **extra), args.repeat)
     flops = 2.0 * T * T * args.heads * args.head_dim        # causal: half of 4*T*T*h*d
     from . import tensorcore
     return {"kernel": "attention_prefill_mma" if args.mma_sync else "attention_prefill_tcgen05",
@@ -233,6 +256,8 @@ def main(argv=None) -> int:
         p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=64)
         p.add_argument("--splits", type=int, default=0)
+        p.add_argument("--shared-rows", action="store_true",
+                       help="one pool head for all query heads, rows as keys and values, a sink per head")
         p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
         p.add_argument("--cluster-merge", action="store_true", help="with --splits <= 8: merge inside the kernel")
         p.add_argument("--cp-async", action="store_true", help="decode: key and value tiles by cp.async, not TMA")

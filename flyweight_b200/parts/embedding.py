@@ -42,6 +42,14 @@ class HashedPairEmbedding(Embedding):
     def state_spec(self):
         return FixedState((1,), torch.int32)
 
+    def plan(self, builder, table, vocab, cache):
+        """The same operation for the native step plan."""
+        from ..engine.plan import NotPlannable
+        if cache is None or cache.state is None:
+            raise NotPlannable("the hashed pair embedding has no state slot")
+        builder.embed_pairs(table, self.pairs, vocab, self.buckets, self.mul_prev, self.mul_cur, self.scale,
+                            cache.state)
+
     def forward(self, ctx, table, cache):
         pairs = self.pairs if self.pairs.dtype == table.dtype else self.pairs.to(table.dtype)
         return latent_kernels.embed_pair_hash(table, pairs, ctx.batch, cache.state, self.buckets,

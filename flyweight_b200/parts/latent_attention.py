@@ -118,6 +118,29 @@ class LatentAttention(Mixer):
     def prepare(self, max_positions, device):
         self.position.prepare(max_positions, device)
 
+    def plan_stream(self, builder, h, cache, out):
+        """The same operations for the native step plan: ``h`` (a buffer in the activation dtype) in,
+        the mixer's output into ``out`` (fp32)."""
+        from ..engine.plan import NotPlannable
+        rotation = self.position.rotation()
+        if rotation is None:
+            raise NotPlannable(f"position encoding {self.position.kind!r} is no plain rotation")
+        table, rot_dims, pairing = rotation
+        act = builder.act_dtype
+        proj = builder.tokens(self.w_in.shape[0], act)
+        builder.linear(h, self.w_in, proj, "queries | latent")
+        qa = builder.tokens(self.n_heads * self.row, act)
+        builder.latent_prepare(proj, self.q_width, self.norm_w, table, qa, cache, not self.shares_cache,
+                               self.n_heads, self.dim, self.rot, rot_dims, pairing, self.rank, self.row, self.eps)
+        builder.head_linear(proj, self.dim + self.rot, self.w_uk_t, qa, self.row, "queries into the latent's space")
+        builder.free(proj)
+        heads_out = builder.tokens(self.n_heads * self.vdim, act)
+        builder.latent_attention(qa, cache, self.sink, self.w_uv, heads_out, self.n_heads, self.rank,
+                                 self.rank + self.rot, self.row, self.scale)
+        builder.free(qa)
+        builder.linear(heads_out, self.w_o, out, "latent attention out")
+        builder.free(heads_out)
+
     def forward(self, ctx, h, cache):
         act = ctx.precision.act_dtype
         batch = ctx.batch

@@ -31,6 +31,32 @@ class OutputNormResidual(Arrangement):
     def stateful_parts(self):
         return tuple(part for part in (self.mixer, self.shift) if part is not None)
 
+    def plan(self, builder, cache):
+        """This layer's operations for the native step plan (the symbolic twin of ``forward``)."""
+        from ..engine.plan import NotPlannable
+        if self.shift is None or getattr(self.shift, "plan", None) is None:
+            raise NotPlannable("the output-norm arrangement has a native form with a stream shift only")
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and getattr(part, "plan_stream", None) is None:
+                raise NotPlannable(f"part {part.kind!r} has no native form behind an unnormed stream")
+        for norm in (self.mixer_out_norm, self.ffn_out_norm):
+            if norm is not None and getattr(norm, "gain", None) is None:
+                raise NotPlannable(f"norm {norm.kind!r} has no native form behind a sublayer")
+        act = builder.act_dtype
+        h = builder.tokens(builder.hidden, act)
+        self.shift.plan(builder, h, cache)
+        y = builder.delta                      # a sublayer's output, fp32; the norm behind it adds it into x
+        self.mixer.plan_stream(builder, h, cache, y)
+        builder.free(h)
+        if self.feed_forward is None:
+            builder.gain_add(y, self.mixer_out_norm.gain, self.mixer_out_norm.eps, None)
+            return
+        copy = builder.tokens(builder.hidden, act) if act != torch.float32 else None
+        builder.gain_add(y, self.mixer_out_norm.gain, self.mixer_out_norm.eps, copy)
+        self.feed_forward.plan_stream(builder, builder.x if copy is None else copy, y)
+        builder.free(copy)
+        builder.gain_add(y, self.ffn_out_norm.gain, self.ffn_out_norm.eps, None)
+
     def forward(self, ctx, x, pending, cache):
         if pending is not None:
             ops.add_(x, pending)

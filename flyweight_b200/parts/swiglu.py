@@ -61,6 +61,14 @@ class SwiGLU(FeedForward):
             a = ops.silu_mul(gate_up, act)
         return ops.linear_into_residual(a, self.w_down, residual)
 
+    def plan_stream(self, builder, h, out):
+        """For an arrangement without a norm in front: gate|up with silu(g)*u from the buffer ``h``, down
+        into ``out`` (fp32)."""
+        a = builder.tokens(self.ffn_dim, builder.act_dtype)
+        builder.swiglu(h, self.w_gate_up, a, "gate|up")
+        builder.linear(a, self.w_down, out, "down")
+        builder.free(a)
+
     def plan(self, builder, norm):
         """Norm, gate|up with silu(g)*u, down with the residual sum, for the native step plan."""
         from ..engine.plan import EPI_SWIGLU

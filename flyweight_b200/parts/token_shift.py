@@ -31,5 +31,9 @@ class TokenShift(StreamShift):
     def state_spec(self):
         return FixedState((self.size,))
 
+    def plan(self, builder, out, cache):
+        """The same operation for the native step plan: the shifted stream into ``out``."""
+        builder.token_shift(self.weight, cache.state, out)
+
     def forward(self, ctx, x, cache):
         return latent_kernels.token_shift(x, self.weight, cache.state, ctx.batch, ctx.precision.act_dtype)

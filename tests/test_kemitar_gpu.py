@@ -13,7 +13,7 @@ from gpu_util import (DTYPES, TOL_ORACLE, assert_close, mixed_trace, model_dir, 
 from tiny_configs import TINY, vocab_of
 
 pytestmark = pytest.mark.gpu
-NAMES = ("KA", "KB")
+NAMES = ("KA", "KB", "KC")
 
 
 @pytest.mark.parametrize("name", NAMES)

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from gpu_util import engine_model, mixed_trace, random_tokens
-from tiny_configs import TINY, make_model_dir
+from tiny_configs import TINY, make_model_dir, vocab_of
 
 pytestmark = pytest.mark.gpu
 
@@ -63,6 +63,31 @@ def test_tiny_models_step_for_step(name, dtype):
         r.cache.check()
         r.check_health()
     assert runners[1].step_plan.n_ops > 10
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_kemitar_step_for_step(dtype):
+    """The hashed pair embedding, the token shift, latent attention (tcgen05, tiled and decode kernels with
+    a sink; the fp32 kernel) and the output norms as operations of the plan: the same bits, the same
+    cache rows and the same per-request state (last token, shift rows) as the parts' ``forward``."""
+    name = "KC"
+    runners = pair_of_runners(engine_model(name, dtype))
+    same_steps(runners, counted_steps(name, [150], 1), f"{name} {dtype} whole")
+    same_steps(runners, counted_steps(name, [1, 1, 2, 15, 16, 17, 31, 33, 64, 65, 1, 1, 128, 129, 3], 2),
+               f"{name} {dtype} portions")
+    steps, _ = mixed_trace([70, 150, 33, 200, 90, 130], vocab_of(TINY[name]), num_pages=9, seed=4, tail=20)
+    same_steps(runners, steps, f"{name} {dtype} mixed")
+    for r in runners:
+        r.cache.check()
+        r.check_health()
+    assert runners[1].step_plan.n_ops > 10
+
+
+def test_a_kemitar_model_with_other_heads_in_every_layer_keeps_the_python_path():
+    from flyweight_b200.engine import ModelRunner
+    model = engine_model("KA", "bfloat16")
+    runner = ModelRunner(model, num_pages=4, num_slots=2, max_model_len=128, max_batched_tokens=128)
+    assert runner.step_plan is None and "row tiles" in model.not_plannable
 
 
 def test_decoding_requests_at_the_head_of_a_step_beside_portions():

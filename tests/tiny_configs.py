@@ -89,7 +89,19 @@ KEMITAR_B = {
     ],
 }
 
-TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B})
+# One head count in every layer (the native step plan cuts a step's prompts into row tiles once for all
+# layers), a cache row of 96 + 32 = 128 entries, a layer that reads the rows of the one before.
+KEMITAR_C = {
+    "architecture": "Kemitar", "vocab": 300, "width": 128, "norm": {"eps": 1e-5},
+    "embedding": {"scale": 2.0, "bigram": {"buckets": 61, "mul_prev": 13, "mul_cur": 3}},
+    "layers": [
+        _kemitar_layer(_latent(4, 32, 32, 16, 96, 10000.0, 0.125), 256),
+        _kemitar_layer(_latent(4, 16, 32, 32, 96, 10000.0, 0.15, kv_from=0), None),
+        _kemitar_layer(_latent(4, 16, 16, 16, 40, 500.0, 0.2), 192),
+    ],
+}
+
+TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B, "KC": KEMITAR_C})
 
 
 def vocab_of(config: dict) -> int:
