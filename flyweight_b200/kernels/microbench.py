@@ -111,8 +111,9 @@ def run_attention_decode(args) -> dict:
         splits, per, in_cluster = args.splits, -(-width // args.splits), args.cluster_merge
     scale = 1.0 / math.sqrt(args.head_dim)
     ops.set_decode_attention_tma(not args.cp_async, args.stages)
-    us = _time(lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
-                                                args.heads, 0, scale, splits, per, in_cluster, **extra), args.repeat)
+    call = lambda: ops.attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, table,
+                                           args.heads, 0, scale, splits, per, in_cluster, **extra)
+    us = _time_graph(call, args.repeat) if args.graph else _time(call, args.repeat)
     ops.set_decode_attention_tma(True)
     kv_bytes = B * ctx * args.kv_heads * args.head_dim * 2 * (1 if args.shared_rows else 2)
     from . import tensorcore
@@ -258,6 +259,8 @@ def main(argv=None) -> int:
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--shared-rows", action="store_true",
                        help="one pool head for all query heads, rows as keys and values, a sink per head")
+        p.add_argument("--graph", action="store_true",
+                       help="decode: the launches captured in a CUDA graph (kernels shorter than a Python call)")
         p.add_argument("--mma-sync", action="store_true", help="the mma.sync prompt kernel")
         p.add_argument("--cluster-merge", action="store_true", help="with --splits <= 8: merge inside the kernel")
         p.add_argument("--cp-async", action="store_true", help="decode: key and value tiles by cp.async, not TMA")

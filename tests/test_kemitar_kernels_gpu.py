@@ -382,7 +382,7 @@ def test_per_head_products(dtype, T, heads, N, K):
     assert float((got[:, :, N:] - 7.0).abs().max()) == 0.0 and float((y[:, :y_col].float() - 7.0).abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("heads,row", [(8, 128), (20, 64), (17, 48), (40, 128), (128, 64)])
+@pytest.mark.parametrize("heads,row", [(8, 128), (20, 64), (17, 48), (40, 128), (128, 64), (12, 96), (6, 80)])
 @pytest.mark.parametrize("new", [1, 3, 70, 200])
 def test_paged_attention_with_a_sink_and_one_shared_pool_head(heads, row, new):
     """Many query heads over one pool head whose rows are keys and values, with a sink per head: the
