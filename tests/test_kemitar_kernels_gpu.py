@@ -284,15 +284,16 @@ def test_a_layer_that_reads_another_layers_rows(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("far", [0, 1, 63, 64, 65, 127, 128, 300, 511, 512])
-def test_one_key_that_stands_out_is_found_wherever_it_lies(dtype, far):
+@pytest.mark.parametrize("far,n", [(0, 600), (1, 600), (63, 600), (64, 600), (65, 600), (127, 600), (128, 600),
+                                   (300, 600), (511, 600), (512, 600), (599, 600), (0, 1), (0, 2), (1, 2), (62, 63),
+                                   (63, 64), (0, 64), (63, 65), (64, 65), (127, 128), (128, 129), (64, 129)])
+def test_one_key_that_stands_out_is_found_wherever_it_lies(dtype, far, n):
     """Random scores hide a lost key among hundreds: here the query at the end matches one key far
     more than any other, so the output is that key's value unless the key was skipped -- at a page's
     first and last row, in the first page, in the last, for a prompt and for a decoded token."""
     from flyweight_b200.kernels import latent
     heads, rank, rot, row = 6, 48, 16, 64
-    n = 600
-    g = torch.Generator().manual_seed(far)
+    g = torch.Generator().manual_seed(far + n)
     keys = torch.randn(n, row, generator=g, dtype=F64) * 0.3
     keys[:, rank + rot:] = 0
     query = torch.randn(heads, row, generator=g, dtype=F64) * 0.3
@@ -314,9 +315,9 @@ def test_one_key_that_stands_out_is_found_wherever_it_lies(dtype, far):
     for i, page in enumerate(pages):
         chunk = keys[i * 64:(i + 1) * 64]
         pool[page, 0, :chunk.shape[0]] = chunk
-    table = torch.tensor([pages], dtype=torch.int32)
+    table = torch.tensor([pages[:max(1, -(-n // 64))]], dtype=torch.int32)
     rel = 1e-5 if dtype == torch.float32 else 2.0 ** -7
-    for new in (1, 40):            # the last token alone (decoding), and as the last of a portion
+    for new in sorted({1, min(40, n)}):   # the last token alone (decoding), and as the last of a portion
         batch = make_batch([n], [new], table=table)
         qa = torch.zeros(new, heads, row, dtype=F64)
         qa[-1] = query
@@ -425,3 +426,50 @@ def test_paged_attention_with_a_sink_and_one_shared_pool_head(heads, row, new):
             want = (p @ keys[:pos + 1]) / (p.sum(dim=1) + torch.exp(sink - top))[:, None]
             close(out[at + j], want, 2.0 ** -7, f"sequence {i} position {pos}")
         at += m
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("at", [0, 5, 62, 63, 64, 100])
+def test_a_key_behind_the_query_is_not_seen(dtype, at):
+    """Inside one portion the query of token ``at`` matches the key of token ``at + 1`` far more than any
+    other: a kernel that let it look ahead would return that key's value."""
+    from flyweight_b200.engine import StepContext
+    from flyweight_b200.kernels import attention, latent
+    heads, rank, rot, row, n = 4, 48, 16, 64, 130
+    g = torch.Generator().manual_seed(at)
+    keys = torch.randn(n, row, generator=g, dtype=F64) * 0.3
+    keys[:, rank + rot:] = 0
+    query = torch.randn(heads, row, generator=g, dtype=F64) * 0.3
+    query[:, rank + rot:] = 0
+    query[1] *= 6.0 / query[1].norm()
+    keys[at + 1, :rank + rot] = 4.0 * query[1, :rank + rot] / query[1, :rank + rot].norm()
+    if dtype == torch.bfloat16:
+        keys, query = bf16_round(keys), bf16_round(query)
+    sink = torch.tensor([0.0, -2.0, 1.0, 0.5], dtype=F64)
+    scores = query @ keys[:at + 1].T
+    top = torch.maximum(scores.max(dim=1).values, sink)
+    p = torch.exp(scores - top[:, None])
+    want = (p @ keys[:at + 1, :rank]) / (p.sum(dim=1) + torch.exp(sink - top))[:, None]
+    pool = torch.full((4, 1, 64, row), float("nan"), dtype=F64)
+    for i, page in enumerate((2, 0, 3)):
+        chunk = keys[i * 64:(i + 1) * 64]
+        pool[page, 0, :chunk.shape[0]] = chunk
+    batch = make_batch([n], [n], table=torch.tensor([[2, 0, 3]], dtype=torch.int32))
+    qa = torch.zeros(n, heads, row, dtype=F64)
+    qa[at] = query
+    rel = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    out = latent.latent_attention(dev(qa, dtype), dev(pool, dtype), dev(sink, torch.float32), batch,
+                                  batch.block_tables[0], rank, rank + rot, 1.0)
+    close(out.view(n, heads, -1)[at, :, :rank], want, rel, f"query {at}")
+    if dtype == torch.bfloat16:
+        cache = type("Cache", (), {})()
+        cache.k_pool, cache.v_pool = dev(pool, dtype), None
+        for tiled in (False, True):
+            attention.force_tiled(tiled)
+            try:
+                out = attention.paged_attention(StepContext(batch, None, DEV), dev(qa, dtype).view(n, -1), cache,
+                                                batch.block_tables[0], heads, 0, 1.0, dtype,
+                                                sink=dev(sink, torch.float32))
+            finally:
+                attention.force_tiled(False)
+            close(out.view(n, heads, -1)[at, :, :rank], want, rel, f"query {at}, paged")
