@@ -18,7 +18,9 @@
 //                         the shared key part, write of the cache row (one pass over the projection)
 //   fwb_head_linear       Y[t][h] = W[h] X[t][h] for every head, fp32 FMA (any sizes, any strides)
 //   fwb_latent_attention_simt   the attention in fp32 arithmetic, any sizes: the 32-bit path
-// The tensor-core forms for bfloat16 are in latent_attention_mma.cu.
+// In bfloat16 the per-head products run on tensor cores (head_linear_mma.cu) and the attention on the
+// paged attention kernels (attention_tcgen05.cu, attention_mma.cu: one pool head that every query head
+// reads, its rows keys and values at once, a sink per head).
 #include "common.cuh"
 
 using namespace fwb;

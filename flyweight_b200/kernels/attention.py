@@ -2,9 +2,10 @@
 
 bfloat16 cache and a shape the tensor-core kernels take: a step of single decode tokens runs
 the split-context decode kernel; prompt portions that fill 128-row tiles run the tcgen05 kernel
-(head sizes 64 and 128); anything else the tiled mma.sync kernel.  Everything else
-(the 32-bit path, head sizes above 128, more than 16 query heads per KV head) runs the SIMT
-kernel.
+(head sizes 64 and 128); anything else the tiled mma.sync kernel.  More than 16 query heads per
+pool head are cut into groups of at most 16 that share the pool head (``head_groups``); a cache with
+one pool holds rows that are keys and values at once; a sink per head may join the softmax.
+Everything else (the 32-bit path, head sizes above 128) runs the SIMT kernel.
 """
 from __future__ import annotations
 

@@ -473,3 +473,36 @@ def test_a_key_behind_the_query_is_not_seen(dtype, at):
             finally:
                 attention.force_tiled(False)
             close(out.view(n, heads, -1)[at, :, :rank], want, rel, f"query {at}, paged")
+
+
+@pytest.mark.parametrize("heads,row,n", [(8, 128, 9000), (20, 64, 12000)])
+def test_a_long_context_cut_into_more_slices_than_a_cluster_holds(heads, row, n):
+    """One decoded token over thousands of rows: the context is cut into more than eight slices, which are
+    merged by the kernel of their own; the sink must still count once."""
+    from flyweight_b200.engine import StepContext
+    from flyweight_b200.kernels import attention
+    g = torch.Generator().manual_seed(n)
+    keys = bf16_round(torch.randn(n, row, generator=g, dtype=F64) * 0.5)
+    q = bf16_round(torch.randn(1, heads, row, generator=g, dtype=F64))
+    sink = torch.randn(heads, generator=g, dtype=F64) * 3.0 + 4.0      # heavy sinks: counted twice, they would show
+    n_pages = -(-n // 64)
+    order = torch.randperm(n_pages + 3, generator=g).tolist()[:n_pages]
+    pool = torch.full((n_pages + 3, 1, 64, row), float("nan"), dtype=F64)
+    for i, page in enumerate(order):
+        chunk = keys[i * 64:(i + 1) * 64]
+        pool[page, 0, :chunk.shape[0]] = chunk
+    batch = make_batch([n], [1], table=torch.tensor([order], dtype=torch.int32))
+    groups = attention.head_groups(heads, 1)
+    splits, _, in_cluster = attention.decode_splits(1, groups, n_pages, row)
+    assert splits > 8 and not in_cluster
+    cache = type("Cache", (), {})()
+    cache.k_pool, cache.v_pool = dev(pool, torch.bfloat16), None
+    scale = 0.2
+    out = attention.paged_attention(StepContext(batch, None, DEV), dev(q, torch.bfloat16).view(1, -1), cache,
+                                    batch.block_tables[0], heads, 0, scale, torch.bfloat16,
+                                    sink=dev(sink, torch.float32)).view(heads, row).float().cpu().to(F64)
+    scores = (q[0] @ keys.T) * scale
+    top = torch.maximum(scores.max(dim=1).values, sink)
+    p = torch.exp(scores - top[:, None])
+    want = (p @ keys) / (p.sum(dim=1) + torch.exp(sink - top))[:, None]
+    close(out, want, 2.0 ** -7, "one token over a long context")
