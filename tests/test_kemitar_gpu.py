@@ -53,7 +53,7 @@ def test_portions_of_any_size(name, dtype, sizes):
                  f"portions {sizes}")
 
 
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ("KD",))
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_unequal_requests_in_one_batch_over_a_small_pool(name, dtype):
     """Up to four live requests, portions beside single tokens, requests left out of steps; the pool

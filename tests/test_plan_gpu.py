@@ -65,12 +65,12 @@ def test_tiny_models_step_for_step(name, dtype):
     assert runners[1].step_plan.n_ops > 10
 
 
+@pytest.mark.parametrize("name", ["KC", "KD"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_kemitar_step_for_step(dtype):
+def test_kemitar_step_for_step(name, dtype):
     """The hashed pair embedding, the token shift, latent attention (tcgen05, tiled and decode kernels with
     a sink; the fp32 kernel) and the output norms as operations of the plan: the same bits, the same
     cache rows and the same per-request state (last token, shift rows) as the parts' ``forward``."""
-    name = "KC"
     runners = pair_of_runners(engine_model(name, dtype))
     same_steps(runners, counted_steps(name, [150], 1), f"{name} {dtype} whole")
     same_steps(runners, counted_steps(name, [1, 1, 2, 15, 16, 17, 31, 33, 64, 65, 1, 1, 128, 129, 3], 2),

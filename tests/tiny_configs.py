@@ -101,7 +101,17 @@ KEMITAR_C = {
     ],
 }
 
-TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B, "KC": KEMITAR_C})
+# Twenty heads in every layer: more than one group of sixteen shares the cached row.
+KEMITAR_D = {
+    "architecture": "Kemitar", "vocab": 180, "width": 96, "norm": {"eps": 1e-5},
+    "embedding": {"scale": 1.5, "bigram": {"buckets": 29, "mul_prev": 7, "mul_cur": 11}},
+    "layers": [
+        _kemitar_layer(_latent(20, 16, 16, 8, 48, 10000.0, 0.18), 128),
+        _kemitar_layer(_latent(20, 8, 16, 16, 48, 10000.0, 0.2, kv_from=0), 160),
+    ],
+}
+
+TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B, "KC": KEMITAR_C, "KD": KEMITAR_D})
 
 
 def vocab_of(config: dict) -> int:
