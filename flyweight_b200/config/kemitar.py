@@ -67,7 +67,14 @@ class KemitarConfig:
             if layer["type"] != "latent_attention":
                 raise ConfigError(f"Kemitar config.json: {where} has the unknown type {layer['type']!r} "
                                   "(known: latent_attention)")
+            layer = copy.deepcopy(dict(layer))
             mixer = layer["mixer"]
+            given = mixer.get("kv_from") if isinstance(mixer, Mapping) else None
+            if isinstance(given, int) and 0 <= given < index:
+                # what a layer that reads another's rows does not state about them is the source's
+                for key in ("kv_rank", "rot_dim", "rot"):
+                    if mixer.get(key) is None and layers[given]["mixer"].get(key) is not None:
+                        mixer[key] = copy.deepcopy(layers[given]["mixer"][key])
             _need(mixer, ("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "rot"), f"{where}'s mixer")
             _need(mixer["rot"], ("base", "dims"), f"{where}'s mixer.rot")
             if int(mixer["rot"]["dims"]) > int(mixer["rot_dim"]) or int(mixer["rot"]["dims"]) % 2:
@@ -88,7 +95,7 @@ class KemitarConfig:
                 if mlp["kind"] != "dense":
                     raise ConfigError(f"Kemitar config.json: {where} has the unknown feed-forward "
                                       f"{mlp['kind']!r} (known: dense)")
-            layers.append(copy.deepcopy(dict(layer)))
+            layers.append(layer)
         known = {"architecture", "architectures", "vocab", "width", "norm", "embedding", "layers"}
         return cls(vocab=int(raw["vocab"]), width=int(raw["width"]), norm_eps=float(raw["norm"]["eps"]),
                    embedding_scale=float(raw["embedding"]["scale"]), bigram=bigram, layers=tuple(layers),
@@ -112,10 +119,16 @@ class KemitarConfig:
             return PartSpec("rms_gain", {"size": W, "eps": eps}, {"weight": name})
 
         layers = []
+        unused = [] if self.bigram is not None else ["bigram"]
         for index, layer in enumerate(self.layers):
             prefix = f"l{index}."
             m = layer["mixer"]
             shares = m.get("kv_from") is not None
+            # a checkpoint may carry a left-out sublayer's tensors all the same; they are passed over
+            if shares:
+                unused += [prefix + "mix.dkv", prefix + "mix.dkv.norm"]
+            if layer.get("mlp") is None:
+                unused += [prefix + name for name in ("norm2", "mlp.gate", "mlp.up", "mlp.down")]
             tensors = {"q": prefix + "mix.q", "uk": prefix + "mix.uk", "uv": prefix + "mix.uv",
                        "o": prefix + "mix.o", "sink": prefix + "mix.sink"}
             if not shares:
@@ -147,6 +160,6 @@ class KemitarConfig:
             head_tensor="head", layers=tuple(layers),
             schedule=tuple(ScheduleEntry(i, cache_of=layer["mixer"].get("kv_from"))
                            for i, layer in enumerate(self.layers)),
-            embedding_scale=self.embedding_scale, embedding=embedding)
+            embedding_scale=self.embedding_scale, embedding=embedding, unused_tensors=tuple(unused))
         spec.validate()
         return spec

@@ -47,7 +47,7 @@ def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
         # sizes the config only states through a rule may be read off the stored tensors instead
         config = reconcile(stored_shapes(model_dir))
     model = arch.model_class(config, parse_dtype(dtype), torch.device(device))
-    model.load(load_checkpoint(model_dir, model.declare()))
+    model.load(load_checkpoint(model_dir, model.declare(), model.spec.unused_tensors))
     return model
 
 

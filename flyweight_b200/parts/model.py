@@ -57,7 +57,7 @@ class DecoderModel:
 
     def load(self, stored: Mapping[str, torch.Tensor]) -> None:
         """Bind checkpoint tensors by name; one error lists everything that does not fit."""
-        tensors = bind_tensors(self.declare(), stored)
+        tensors = bind_tensors(self.declare(), stored, self.spec.unused_tensors)
         get: Callable[[str], torch.Tensor] = tensors.__getitem__
         spec, precision, device = self.spec, self.precision, self.device
         self.embedding = precision.matrix(get(spec.embedding_tensor), device)

@@ -13,7 +13,7 @@ float32 mode of the engine widens (exactly) when it binds.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Mapping, Tuple
+from typing import Dict, Iterable, Mapping, Tuple
 
 import torch
 
@@ -60,10 +60,13 @@ _FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
 _INTS = (torch.int32, torch.int64, torch.int8, torch.uint8)
 
 
-def bind(declared: Mapping[str, TensorDecl],
-         stored: Mapping[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+def bind(declared: Mapping[str, TensorDecl], stored: Mapping[str, torch.Tensor],
+         unused: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+    """``unused``: names a checkpoint of the architecture may carry although this configuration has no
+    use for them (the tensors of a sublayer that a layer leaves out); they are passed over."""
+    unused = set(unused)
     missing = [name for name in declared if name not in stored]
-    unexpected = [name for name in stored if name not in declared]
+    unexpected = [name for name in stored if name not in declared and name not in unused]
     wrong_shape, wrong_dtype = [], []
     out: Dict[str, torch.Tensor] = {}
     for name, decl in declared.items():
@@ -94,5 +97,6 @@ def bind(declared: Mapping[str, TensorDecl],
     return out
 
 
-def load_checkpoint(model_dir, declared: Mapping[str, TensorDecl]) -> Dict[str, torch.Tensor]:
-    return bind(declared, load_model_tensors(model_dir))
+def load_checkpoint(model_dir, declared: Mapping[str, TensorDecl],
+                    unused: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+    return bind(declared, load_model_tensors(model_dir), unused)

@@ -111,3 +111,27 @@ def test_the_sink_takes_weight_from_the_keys():
     scores = torch.zeros(1, 2, 2, dtype=torch.float64)
     weights = P.softmax_with_sink(scores, torch.tensor([0.0], dtype=torch.float64))
     assert torch.allclose(weights[0], torch.tensor([[0.5, 0.0], [1 / 3, 1 / 3]], dtype=torch.float64))
+
+
+def test_tensors_of_a_sublayer_that_a_layer_leaves_out_are_passed_over():
+    """A checkpoint may carry the output norm of a feed-forward that a layer does not have, or the latent
+    projection of a layer that reads another's rows; anything else that is not declared is refused."""
+    from flyweight_b200.models import KemitarForCausalLM
+    from flyweight_b200.parts import Precision
+    from flyweight_b200.weights import WeightError, bind, random_tensors
+    model = KemitarForCausalLM(typed(TINY["KA"]), Precision("float32"), torch.device("cpu"))
+    declared = model.declare()
+    stored = dict(random_tensors(declared, 1, "unit", torch.float32, "cpu"))
+    stored["l1.norm2"] = torch.ones(())
+    stored["l1.mix.dkv"] = torch.zeros(48, 80)
+    assert set(bind(declared, stored, model.spec.unused_tensors)) == set(declared)
+    stored["l0.norm3"] = torch.ones(())
+    with pytest.raises(WeightError, match="l0.norm3"):
+        bind(declared, stored, model.spec.unused_tensors)
+
+
+def test_a_layer_that_reads_anothers_rows_may_leave_their_sizes_unsaid():
+    raw = copy.deepcopy(TINY["KA"])
+    for key in ("kv_rank", "rot_dim", "rot"):
+        raw["layers"][1]["mixer"].pop(key)
+    assert typed(raw).to_dict() == TINY["KA"]
