@@ -271,7 +271,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         head[h] = kvh * group + (valid ? r % group : 0);
         const int pos = positions[tok[h]];
         hi[h] = valid ? pos : -1;                           // an invalid row sees no key
-        lo[h] = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+        lo[h] = fwb::first_visible_key(pos, window);
         qrow[h] = valid ? q + ((size_t)tok[h] * nh + head[h]) * HD : nullptr;
     }
     uint32_t qf[HD / 16][4];
@@ -279,7 +279,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 
     // keys this CTA walks: from the lowest key any row may see to the position of its last token
     const int pos_first = positions[tok0], pos_last = positions[tok0 + n_tok - 1];
-    const int lo_block = window > 0 ? (pos_first - window + 1 > 0 ? pos_first - window + 1 : 0) : 0;
+    const int lo_block = fwb::first_visible_key(pos_first, window);
     const int tile_begin = lo_block / KEYS, tile_end = pos_last / KEYS + 1;
 
     float o[HD / 8][4];
@@ -439,7 +439,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // of a slice that does not hold the token itself is fetched before the wait for the previous
     // kernel (which writes this step's keys and the queries)
     const int pos = positions[tok];
-    const int lo_key = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+    const int lo_key = fwb::first_visible_key(pos, window);
     const int* table = block_table + (size_t)tok_seg[tok] * max_pages;
     const int first_tile = lo_key / KEYS, last_tile = pos / KEYS;
     const int tile_begin = first_tile + split * tiles_per_split;

@@ -39,7 +39,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[t];
     const int* table = block_table + (size_t)tok_seg[t] * max_pages;
-    const int lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+    const int lo = fwb::first_visible_key(pos, window);
 
     for (int i = threadIdx.x; i < group * hd; i += blockDim.x)
         qs[i] = to_f32<TQ>(q[((size_t)t * nh + (size_t)kvh * group) * hd + i]);

@@ -113,7 +113,7 @@ __device__ __forceinline__ Item load_item(const AttnParams& prm, int w) {
     it.rows = n_tok * prm.group;
     it.pos_first = prm.positions[it.tok0];
     it.pos_last = prm.positions[it.tok0 + n_tok - 1];
-    const int lo_block = prm.window > 0 ? (it.pos_first - prm.window + 1 > 0 ? it.pos_first - prm.window + 1 : 0) : 0;
+    const int lo_block = fwb::first_visible_key(it.pos_first, prm.window);
     it.tile_begin = lo_block / KEYS;
     it.n_tiles = it.pos_last / KEYS + 1 - it.tile_begin;
     it.table = prm.block_table + (size_t)seg * prm.max_pages;
@@ -296,7 +296,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             const int head = item.kvh * prm.group + (valid ? row % prm.group : 0);
             const int pos = prm.positions[tok];
             const int hi = valid ? pos : -1;               // a row without a token sees no key
-            const int lo = prm.window > 0 ? (pos - prm.window + 1 > 0 ? pos - prm.window + 1 : 0) : 0;
+            const int lo = fwb::first_visible_key(pos, prm.window);
             {
                 // every matrix product that read the previous item's Q has completed: that item's
                 // O has been taken
@@ -320,7 +320,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 l = 1.0f;
             }
             // the highest lower bound of the keys any row of this item may see
-            const int lo_max = prm.window > 0 ? (item.pos_last - prm.window + 1 > 0 ? item.pos_last - prm.window + 1 : 0) : 0;
+            const int lo_max = fwb::first_visible_key(item.pos_last, prm.window);
             for (int j = 0; j < item.n_tiles; ++j) {
                 const int g = g0 + j, key0 = (item.tile_begin + j) * KEYS, buf = g & 1;
                 ok = mbar_wait(&s_ready[buf], (g >> 1) & 1, abort_flag, 16, prm.status);

@@ -113,6 +113,21 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// The lowest position a query at `pos` may see, from the one mask parameter every attention kernel
+// takes.  span > 0: a sliding window, the last `span` positions up to pos.  span < 0: the sequence is
+// cut into runs of -span positions counted from position 0, and a query sees only the keys of its own
+// run (up to itself).  span == 0: every key from position 0 on.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int span) {
+    if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+    if (span < 0) return pos - pos % (-span);
+    return 0;
+}
+
+// The tanh form of gelu: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float gelu_tanh_f32(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
 // silu(g) = g * sigmoid(g), sigmoid split by sign so neither branch overflows.
 __device__ __forceinline__ float silu_f32(float g) {
     const float e = expf(-fabsf(g));

@@ -1,0 +1,249 @@
+// The gated delta rule: a recurrent mixer whose per-request state is one [d][e] matrix per head.
+//
+// Per token and head, with unit vectors q (times d^-1/2) and k of size d, a value v of size e, a
+// write strength beta in (0, 1) and a decay g in (0, 1):
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// so the read-out sees the token's own write.  q, k and v come from one fused projection
+//     p[t] = [ q: G d | k: G d | v: H e | gate: H e | b: H | a: H ]        (fp32)
+// through a short causal convolution over time per channel (taps [C][L], the last tap on the token
+// itself) and silu; q and k are then made unit vectors per head (x / sqrt(sum x^2 + 1e-6)); query
+// head h uses q/k head h / (H / G).  beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
+//
+// Four kernels (everything fp32):
+//   delta_prepare   one block per token: convolution + silu, unit vectors, beta and g
+//                   -> r[t] = [ q^: G d | k^: G d | v: H e | beta: H | g: H ]
+//   delta_conv_advance  one thread per (segment, channel): the request's last L-1 inputs, for the
+//                   next step (runs behind delta_prepare, which reads the old ones)
+//   delta_scan      one block per (32 columns of S, head, segment): the recurrence over the
+//                   segment's tokens in order.  A column of S evolves independently of the others;
+//                   four adjacent lanes hold one column (d/4 entries each in registers), so a token
+//                   costs two 4-lane reductions.  State in and out of the request's slot.
+//   gated_head_norm out[t][h] = weight * o / sqrt(mean(o^2) + eps) * silu(gate)
+// A request's slot is [ S: H d e | conv inputs: C (L-1) ] fp32, zero when the request starts.  A
+// token's result depends on its request's earlier tokens only through that slot, and every sum runs
+// in an order fixed by the sizes, so it does not depend on how the sequence was cut into steps.
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+struct DeltaShape {
+    int H, G, d, e, L;      // heads, q/k heads, q/k size, value size, taps
+    __host__ __device__ int cq() const { return G * d; }
+    __host__ __device__ int cv() const { return H * e; }
+    __host__ __device__ int channels() const { return 2 * G * d + H * e; }      // through the convolution
+    __host__ __device__ int p_width() const { return channels() + H * e + 2 * H; }
+    __host__ __device__ int r_width() const { return channels() + 2 * H; }
+};
+
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const float* __restrict__ p, const float* __restrict__ taps, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, const float* __restrict__ state, long long slot_stride,
+                     const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                     const int* __restrict__ tok_seg, float* __restrict__ r, DeltaShape sh) {
+    fwb::pdl_entry();
+    extern __shared__ float c[];                  // the token's channels behind convolution and silu
+    const int t = blockIdx.x;
+    const int seg = tok_seg[t];
+    const int local = t - seg_start[seg];         // tokens of this request in front of t in this step
+    const int C = sh.channels(), P = sh.p_width(), R = sh.r_width(), L = sh.L;
+    const float* hist = state + (size_t)seg_slot[seg] * slot_stride + (size_t)sh.H * sh.d * sh.e;
+    for (int ch = threadIdx.x; ch < C; ch += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < L; ++j) {
+            const int back = L - 1 - j;           // tap j multiplies the input `back` tokens ago
+            const float x = back <= local ? p[(size_t)(t - back) * P + ch]
+                                          : hist[(size_t)ch * (L - 1) + (L - 1) - (back - local)];
+            acc = fmaf(taps[(size_t)ch * L + j], x, acc);
+        }
+        c[ch] = silu_f32(acc);
+    }
+    __syncthreads();
+    float* out = r + (size_t)t * R;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const float q_scale = rsqrtf((float)sh.d);
+    for (int unit = warp; unit < 2 * sh.G; unit += warps) {       // G query heads, then G key heads
+        const float* src = c + (size_t)unit * sh.d;
+        float ss = 0.0f;
+        for (int i = lane; i < sh.d; i += 32) ss = fmaf(src[i], src[i], ss);
+        ss = warp_sum(ss);
+        const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (unit < sh.G ? q_scale : 1.0f);
+        for (int i = lane; i < sh.d; i += 32) out[(size_t)unit * sh.d + i] = src[i] * inv;
+    }
+    for (int i = threadIdx.x; i < sh.cv(); i += blockDim.x) out[2 * sh.cq() + i] = c[2 * sh.cq() + i];
+    for (int h = threadIdx.x; h < sh.H; h += blockDim.x) {
+        const float b = p[(size_t)t * P + C + sh.cv() + h];
+        const float a = p[(size_t)t * P + C + sh.cv() + sh.H + h] + dt_bias[h];
+        const float softplus = a > 20.0f ? a : log1pf(expf(a));
+        out[C + h] = 1.0f / (1.0f + expf(-b));
+        out[C + sh.H + h] = expf(-expf(a_log[h]) * softplus);
+    }
+}
+
+__global__ void __launch_bounds__(128)
+delta_conv_advance_kernel(const float* __restrict__ p, float* __restrict__ state, long long slot_stride,
+                          const int* __restrict__ seg_start, const int* __restrict__ seg_slot, DeltaShape sh) {
+    fwb::pdl_entry();
+    const int seg = blockIdx.y;
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= sh.channels()) return;
+    const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0, keep = sh.L - 1, P = sh.p_width();
+    if (n <= 0) return;
+    float* hist = state + (size_t)seg_slot[seg] * slot_stride + (size_t)sh.H * sh.d * sh.e + (size_t)ch * keep;
+    float next[MAX_TAPS];
+    for (int j = 0; j < keep; ++j) {
+        const int local = n - keep + j;           // the input that becomes entry j (oldest first)
+        next[j] = local >= 0 ? p[(size_t)(t0 + local) * P + ch] : hist[j + n];
+    }
+    for (int j = 0; j < keep; ++j) hist[j] = next[j];
+}
+
+template <int DPL>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ r, float* __restrict__ state, long long slot_stride,
+                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ o,
+                  DeltaShape sh) {
+    fwb::pdl_entry();
+    constexpr int DP = 4 * DPL;
+    __shared__ float kq[2][2][DP];
+    __shared__ float vs[2][32];
+    __shared__ float bg[2][2];
+    const int seg = blockIdx.z, h = blockIdx.y;
+    const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
+    if (t1 <= t0) return;
+    const int d = sh.d, e = sh.e, R = sh.r_width();
+    const int kv_head = h / (sh.H / sh.G);
+    const int col_local = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    const int col = blockIdx.x * 32 + col_local;
+    const bool valid = col < e;
+    float* S_slot = state + (size_t)seg_slot[seg] * slot_stride + (size_t)h * d * e;
+    float S[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int dd = sub + 4 * i;
+        S[i] = (valid && dd < d) ? S_slot[(size_t)dd * e + col] : 0.0f;
+    }
+    const int q_at = kv_head * d, k_at = sh.cq() + kv_head * d, v_at = 2 * sh.cq() + h * e;
+    const int beta_at = sh.channels() + h, g_at = sh.channels() + sh.H + h;
+    auto fetch = [&](int t, int buf) {
+        const float* row = r + (size_t)t * R;
+        for (int i = threadIdx.x; i < 2 * DP; i += blockDim.x) {
+            const int which = i / DP, dd = i - which * DP;
+            kq[buf][which][dd] = dd < d ? row[(which ? q_at : k_at) + dd] : 0.0f;
+        }
+        if (threadIdx.x < 32) {
+            const int cc = blockIdx.x * 32 + threadIdx.x;
+            vs[buf][threadIdx.x] = cc < e ? row[v_at + cc] : 0.0f;
+        }
+        if (threadIdx.x == 32) bg[buf][0] = row[beta_at];
+        if (threadIdx.x == 33) bg[buf][1] = row[g_at];
+    };
+    fetch(t0, 0);
+    __syncthreads();
+    for (int t = t0; t < t1; ++t) {
+        const int buf = (t - t0) & 1;
+        if (t + 1 < t1) fetch(t + 1, buf ^ 1);
+        const float beta = bg[buf][0], g = bg[buf][1];
+        const float* k = kq[buf][0];
+        const float* q = kq[buf][1];
+        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            S[i] *= g;
+            part[i & 3] = fmaf(S[i], k[sub + 4 * i], part[i & 3]);
+        }
+        float dot = (part[0] + part[1]) + (part[2] + part[3]);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        const float u = beta * (vs[buf][col_local] - dot);
+        part[0] = part[1] = part[2] = part[3] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            S[i] = fmaf(k[sub + 4 * i], u, S[i]);
+            part[i & 3] = fmaf(S[i], q[sub + 4 * i], part[i & 3]);
+        }
+        float out = (part[0] + part[1]) + (part[2] + part[3]);
+        out += __shfl_xor_sync(0xffffffffu, out, 1);
+        out += __shfl_xor_sync(0xffffffffu, out, 2);
+        if (sub == 0 && valid) o[((size_t)t * sh.H + h) * e + col] = out;
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int dd = sub + 4 * i;
+        if (valid && dd < d) S_slot[(size_t)dd * e + col] = S[i];
+    }
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                       const float* __restrict__ weight, float eps, TO* __restrict__ out, int rows, int H, int e) {
+    fwb::pdl_entry();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int t = row / H, h = row - t * H;
+    const float* src = o + (size_t)row * e;
+    const float* g = gate + (size_t)t * gate_stride + (size_t)h * e;
+    float ss = 0.0f;
+    for (int i = lane; i < e; i += 32) ss = fmaf(src[i], src[i], ss);
+    const float inv = rsqrtf(warp_sum(ss) / (float)e + eps);
+    for (int i = lane; i < e; i += 32)
+        out[(size_t)row * e + i] = from_f32<TO>(((src[i] * inv) * weight[i]) * silu_f32(g[i]));
+}
+
+}  // namespace
+
+// p: [T][2Gd + 2He + 2H] fp32 (q | k | v | gate | b | a).  taps: [2Gd + He][L] fp32.  a_log, dt_bias: [H].
+// state: [slots][slot_stride] fp32 with S at 0 and the convolution's inputs behind it.
+// r: [T][2Gd + He + 2H] fp32 scratch.  o: [T][H][e] fp32.
+FWB_API int fwb_delta_rule(const float* p, const float* taps, const float* a_log, const float* dt_bias,
+                           float* state, long long slot_stride, const int* seg_start, const int* seg_slot,
+                           const int* tok_seg, float* r, float* o, int T, int n_segments, int H, int G, int d,
+                           int e, int L, cudaStream_t stream) {
+    if (T <= 0 || n_segments <= 0) return FWB_OK;
+    if (!p || !taps || !a_log || !dt_bias || !state || !seg_start || !seg_slot || !tok_seg || !r || !o)
+        return FWB_BAD_ARGUMENT;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0 || L < 1) return FWB_BAD_ARGUMENT;
+    if (L > MAX_TAPS || d > 256) return FWB_TOO_LARGE;
+    const DeltaShape sh{H, G, d, e, L};
+    if (slot_stride < (long long)H * d * e + (long long)sh.channels() * (L - 1)) return FWB_BAD_ARGUMENT;
+    const size_t smem = (size_t)sh.channels() * sizeof(float);
+    if (smem > 160 * 1024 || n_segments > 65535 || H > 65535) return FWB_TOO_LARGE;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    fwb::pdl(delta_prepare_kernel, T, 128, smem, stream)(p, taps, a_log, dt_bias, state, slot_stride, seg_start,
+                                                         seg_slot, tok_seg, r, sh);
+    if (L > 1)
+        fwb::pdl(delta_conv_advance_kernel, dim3((sh.channels() + 127) / 128, n_segments), 128, 0, stream)(
+            p, state, slot_stride, seg_start, seg_slot, sh);
+    const dim3 grid((e + 31) / 32, H, n_segments);
+#define FWB_SCAN(DPL) \
+    fwb::pdl(delta_scan_kernel<DPL>, grid, 128, 0, stream)(r, state, slot_stride, seg_start, seg_slot, o, sh)
+    if (d <= 32) FWB_SCAN(8);
+    else if (d <= 64) FWB_SCAN(16);
+    else if (d <= 128) FWB_SCAN(32);
+    else FWB_SCAN(64);
+#undef FWB_SCAN
+    return fwb_launch_status();
+}
+
+// o: [T][H][e] fp32; gate: row t at gate + t * gate_stride, [H][e] fp32; weight: [e]; out: [T][H e].
+FWB_API int fwb_gated_head_norm(const float* o, const float* gate, long long gate_stride, const float* weight,
+                                float eps, void* out, int out_bf16, int T, int H, int e, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!o || !gate || !weight || !out || H <= 0 || e <= 0) return FWB_BAD_ARGUMENT;
+    const long long rows = (long long)T * H;
+    if (rows > 2147483647LL / 4) return FWB_TOO_LARGE;
+    const int blocks = (int)((rows + 3) / 4);
+    if (out_bf16)
+        fwb::pdl(gated_head_norm_kernel<__nv_bfloat16>, blocks, 128, 0, stream)(o, gate, gate_stride, weight, eps,
+                                                                                 (__nv_bfloat16*)out, (int)rows, H, e);
+    else
+        fwb::pdl(gated_head_norm_kernel<float>, blocks, 128, 0, stream)(o, gate, gate_stride, weight, eps,
+                                                                        (float*)out, (int)rows, H, e);
+    return fwb_launch_status();
+}

@@ -104,6 +104,7 @@ struct Params {
     int M, N, K;           // tokens, features (of one accumulator), reduction
     int ldy;
     int up_row_offset;     // SwiGLU: rows of the up projection start here in W
+    int gate_act;          // SwiGLU: the gate's activation (tc5 GATE_SILU | GATE_GELU_TANH)
     int k_blocks_per_split;
     int stages;            // depth of the shared-memory ring (<= Tile::MAX_STAGES)
     int* status;           // the library's status word (see tc5::status_word)
@@ -357,7 +358,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (f + BM < prm.N) reinterpret_cast<__nv_bfloat16*>(prm.y)[at + BM] = __float2bfloat16_rn(u);
         } else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + (splits > 1 ? u : prm.addend[at]);
         else if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
-        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_fast(g) * u);
+        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(gate_act_fast(prm.gate_act, g) * u);
     };
 
     if (splits == 1) {
@@ -529,6 +530,8 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
 FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float* addend, int M, int N,
                              int K, int w_rows, int ldy, int epilogue, int up_row_offset, int splits,
                              int stages, int tile_tokens, int wide, cudaStream_t stream) {
+    const int gate_act = epilogue >> 8;     // bits above the epilogue code: the gate's activation
+    epilogue &= 0xff;
     if (M <= 0 || N <= 0) return FWB_OK;
     if (!X || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
     if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;
@@ -567,6 +570,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.K = K;
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
+    prm.gate_act = gate_act;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
     prm.status = status_word();
@@ -595,6 +599,8 @@ FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, con
                                     const void* W, void* Y, int M, int N, int K, int w_rows, int ldy,
                                     int epilogue, int up_row_offset, int splits, int stages,
                                     int tile_tokens, cudaStream_t stream) {
+    const int gate_act = epilogue >> 8;
+    epilogue &= 0xff;
     if (M <= 0 || N <= 0) return FWB_OK;
     if (!x_res || !norm_w || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
     if ((K & 7) || ((uintptr_t)W & 15) || ((uintptr_t)x_res & 15) || ((uintptr_t)norm_w & 15)) return FWB_UNSUPPORTED;
@@ -618,6 +624,7 @@ FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, con
     prm.K = K;
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
+    prm.gate_act = gate_act;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
     prm.status = status_word();

@@ -53,6 +53,7 @@ struct PairParams {
     void* y;
     int M, N, K, ldy;
     int up_row_offset;
+    int gate_act;          // SwiGLU: the gate's activation (GATE_SILU | GATE_GELU_TANH)
     int token_tiles;
     int* status;
 };
@@ -230,7 +231,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     if (EPI == PAIR_F32) reinterpret_cast<float*>(prm.y)[at] = g[j];
                     else if (EPI == PAIR_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g[j]);
                     else if (EPI == PAIR_SWIGLU_BF16)
-                        reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(silu_fast(g[j]) * u[j]);
+                        reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(gate_act_fast(prm.gate_act, g[j]) * u[j]);
                     else if (EPI == PAIR_F32_WIDE) {
                         reinterpret_cast<float*>(prm.y)[at] = g[j];
                         if (f + PAIR_M < prm.N) reinterpret_cast<float*>(prm.y)[at + PAIR_M] = u[j];
@@ -285,6 +286,8 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const PairParams&
 // CTA pair two blocks of 256 features (plain epilogues only).  K % 8 == 0, bases 16-byte aligned.
 FWB_API int fwb_gemm_tcgen05_pair(const void* X, const void* W, void* Y, int M, int N, int K, int w_rows,
                                   int ldy, int epilogue, int up_row_offset, int wide, cudaStream_t stream) {
+    const int gate_act = epilogue >> 8;     // bits above the epilogue code: the gate's activation
+    epilogue &= 0xff;
     if (M <= 0 || N <= 0) return FWB_OK;
     if (!X || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
     if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;
@@ -299,6 +302,7 @@ FWB_API int fwb_gemm_tcgen05_pair(const void* X, const void* W, void* Y, int M, 
     prm.K = K;
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
+    prm.gate_act = gate_act;
     prm.token_tiles = (M + BN - 1) / BN;
     prm.status = status_word();
     const int features_per_pair = pair_wide(epilogue) ? 2 * PAIR_M : PAIR_M;

@@ -1,0 +1,338 @@
+// Mixture of experts: the router, the sorting of (token, expert) pairs by expert, the experts'
+// gated products over the sorted rows, and the weighted sum.
+//
+//   route    scores s = softmax(router h) over all N router outputs (fp32).  The choice is made on
+//            s + correction: the outputs form n_groups runs of N / n_groups neighbours, a run's value
+//            is its largest choice value, only the `keep` best runs stay in the race (the others count
+//            as minus infinity), and the `top` largest survivors are chosen.  The weights are the plain
+//            s of the chosen, not renormalised.  Ties go to the lower index.
+//   sort     pairs whose output is a real expert (index < E) are counted per expert, the counts are
+//            scanned, every pair gets its row among its expert's rows, and the row tiles of the two
+//            products are listed.  Outputs from E on are identity experts: they have no row.
+//   gemm     one CTA per (row tile of one expert, tile of output features): rows gathered through the
+//            sorted list, fp32 FMA accumulation over k in order.  Form 1: act(x gate^T) * (x up^T) for
+//            the stacked matrix [gate rows | up rows]; form 0: the plain product in fp32.
+//   combine  out[t] = sum over the token's pairs, in slot order, of weight * (expert row | h[t] itself
+//            for an identity expert).
+// A pair's row is a sum over k in a fixed order whatever else is in the step, and a token's pairs are
+// added in slot order, so a token's result does not depend on the batch.  Grids are sized for the
+// worst case from the step's static sizes (every kernel reads the counts on the device), so a step
+// can be captured in a CUDA graph.
+#include "common.cuh"
+
+using namespace fwb;
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;       // tile of the experts' products
+
+template <typename TH>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
+                 int* __restrict__ ids, float* __restrict__ weights, int T, int W, int N, int n_groups, int keep,
+                 int top) {
+    fwb::pdl_entry();
+    extern __shared__ float shared[];             // per warp: s[N], choice[N], group value[n_groups]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = shared + (size_t)warp * (2 * N + n_groups);
+    float* choice = s + N;
+    float* best = choice + N;
+    const TH* row = h + (size_t)t * W;
+    for (int n = 0; n < N; ++n) {
+        const float* w = router + (size_t)n * W;
+        float acc = 0.0f;
+        for (int k = lane; k < W; k += 32) acc = fmaf(to_f32<TH>(row[k]), w[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s[n] = acc;
+    }
+    __syncwarp();
+    float m = -INFINITY;
+    for (int n = lane; n < N; n += 32) m = fmaxf(m, s[n]);
+    m = warp_max(m);
+    float sum = 0.0f;
+    for (int n = lane; n < N; n += 32) sum += expf(s[n] - m);
+    sum = warp_sum(sum);
+    for (int n = lane; n < N; n += 32) {
+        const float v = expf(s[n] - m) / sum;
+        s[n] = v;
+        choice[n] = v + correction[n];
+    }
+    __syncwarp();
+    const int per = N / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+        float v = -INFINITY;
+        for (int j = 0; j < per; ++j) v = fmaxf(v, choice[g * per + j]);
+        best[g] = v;
+    }
+    __syncwarp();
+    // the (n_groups - keep) weakest runs leave the race, weakest first; ties: the higher index leaves
+    for (int round = 0; round < n_groups - keep; ++round) {
+        float v = INFINITY;
+        int at = -1;
+        for (int g = lane; g < n_groups; g += 32)
+            if (best[g] != INFINITY && (best[g] < v || (best[g] == v && g > at))) {
+                v = best[g];
+                at = g;
+            }
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, offset);
+            const int oat = __shfl_xor_sync(0xffffffffu, at, offset);
+            if (oat >= 0 && (at < 0 || ov < v || (ov == v && oat > at))) {
+                v = ov;
+                at = oat;
+            }
+        }
+        if (at < 0) break;
+        __syncwarp();
+        if (lane == 0) best[at] = INFINITY;        // marks a run that is out
+        for (int j = lane; j < per; j += 32) choice[at * per + j] = -INFINITY;
+        __syncwarp();
+    }
+    // the `top` largest choice values, largest first; ties: the lower index
+    for (int slot = 0; slot < top; ++slot) {
+        float v = -INFINITY;
+        int at = -1;
+        for (int n = lane; n < N; n += 32)
+            if (choice[n] > v || at < 0) {
+                if (choice[n] > v || at < 0) {
+                    v = choice[n];
+                    at = n;
+                }
+            }
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, offset);
+            const int oat = __shfl_xor_sync(0xffffffffu, at, offset);
+            if (oat >= 0 && (at < 0 || ov > v || (ov == v && oat < at))) {
+                v = ov;
+                at = oat;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+            ids[(size_t)t * top + slot] = at;
+            weights[(size_t)t * top + slot] = s[at];
+            choice[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// One block.  ids: [A] router outputs of the pairs (A = tokens * top).  Writes
+//   offsets[E + 1]   first row of every expert among the sorted rows
+//   row_token[A]     token of every sorted row
+//   pair_row[A]      sorted row of every pair (-1: an identity expert)
+//   tiles[0]         number of row tiles; tiles[1 + 2 i], tiles[2 + 2 i]: expert and first row of tile i
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int A, int top, int E, int* __restrict__ offsets,
+                int* __restrict__ row_token, int* __restrict__ pair_row, int* __restrict__ tiles) {
+    fwb::pdl_entry();
+    extern __shared__ int counts[];               // [E] counts, then [E] cursors
+    int* cursor = counts + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = ids[a];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, n_tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            const int n = counts[e];
+            offsets[e] = at;
+            cursor[e] = at;
+            for (int row = 0; row < n; row += TM) {
+                tiles[1 + 2 * n_tiles] = e;
+                tiles[2 + 2 * n_tiles] = at + row;
+                ++n_tiles;
+            }
+            at += n;
+        }
+        offsets[E] = at;
+        tiles[0] = n_tiles;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = ids[a];
+        int row = -1;
+        if (e >= 0 && e < E) {
+            row = atomicAdd(&cursor[e], 1);
+            row_token[row] = a / top;
+        }
+        pair_row[a] = row;
+    }
+}
+
+// FORM 1: out[row][f] = act(x . gate_f) * (x . up_f), w: [E][2F][K] (gate rows, then up rows), N = F.
+// FORM 0: out[row][n] = x . w_n, w: [E][N][K], fp32 out.
+// x rows: FORM 1 gathers token rows through row_token; FORM 0 reads sorted rows directly.
+template <typename TX, typename TW, typename TO, int FORM>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                const int* __restrict__ offsets, const int* __restrict__ row_token, const int* __restrict__ tiles,
+                int N, int K, int act) {
+    fwb::pdl_entry();
+    const int tile = blockIdx.y;
+    if (tile >= tiles[0]) return;
+    const int expert = tiles[1 + 2 * tile], row0 = tiles[2 + 2 * tile];
+    const int row_end = offsets[expert + 1];
+    const int n0 = blockIdx.x * TN;
+    __shared__ float xs[TK][TM + 1];
+    __shared__ float ws[FORM ? 2 : 1][TK][TN + 1];
+    __shared__ int src_row[TM];
+    if (threadIdx.x < TM) {
+        const int row = row0 + threadIdx.x;
+        src_row[threadIdx.x] = row < row_end ? (FORM ? row_token[row] : row) : -1;
+    }
+    __syncthreads();
+    const TW* w_gate = w + (size_t)expert * (FORM ? 2 : 1) * N * K;
+    const TW* w_up = w_gate + (size_t)N * K;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;      // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4] = {}, acc2[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += TK) {
+        for (int i = threadIdx.x; i < TM * TK; i += 256) {
+            const int r = i / TK, k = i - r * TK;
+            const int src = src_row[r];
+            xs[k][r] = (src >= 0 && k0 + k < K) ? to_f32<TX>(x[(size_t)src * K + k0 + k]) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < TN * TK; i += 256) {
+            const int n = i / TK, k = i - n * TK;
+            const bool in = n0 + n < N && k0 + k < K;
+            ws[0][k][n] = in ? to_f32<TW>(w_gate[(size_t)(n0 + n) * K + k0 + k]) : 0.0f;
+            if (FORM) ws[1][k][n] = in ? to_f32<TW>(w_up[(size_t)(n0 + n) * K + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < TK; ++k) {
+            float a[4], b[4], b2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b[j] = ws[0][k][tx * 4 + j];
+                if (FORM) b2[j] = ws[1][k][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if (FORM) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row0 + ty * 4 + i;
+        if (row >= row_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (FORM) v = (act == 1 ? gelu_tanh_f32(v) : silu_f32(v)) * acc2[i][j];
+            out[(size_t)row * N + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ pair_row,
+                   const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ out, int W,
+                   int top, int E) {
+    fwb::pdl_entry();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int slot = 0; slot < top; ++slot) {
+            const int a = t * top + slot;
+            const int row = pair_row[a];
+            const float v = row >= 0 ? y[(size_t)row * W + i] : (ids[a] >= E ? to_f32<TH>(h[(size_t)t * W + i]) : 0.0f);
+            acc = fmaf(weights[a], v, acc);
+        }
+        out[(size_t)t * W + i] = acc;
+    }
+}
+
+}  // namespace
+
+// h: [T][W] fp32 or bf16; router: [N][W] fp32; correction: [N] fp32; ids, weights: [T][top].
+FWB_API int fwb_moe_route(const void* h, int h_bf16, const float* router, const float* correction, int* ids,
+                          float* weights, int T, int W, int N, int n_groups, int keep, int top,
+                          cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!h || !router || !correction || !ids || !weights) return FWB_BAD_ARGUMENT;
+    if (W <= 0 || N <= 0 || n_groups <= 0 || N % n_groups || keep <= 0 || keep > n_groups || top <= 0 ||
+        top > keep * (N / n_groups))
+        return FWB_BAD_ARGUMENT;
+    const size_t smem = 4 * (size_t)(2 * N + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) return FWB_TOO_LARGE;
+    const int blocks = (T + 3) / 4;
+    if (h_bf16)
+        fwb::pdl(moe_route_kernel<__nv_bfloat16>, blocks, 128, smem, stream)(
+            (const __nv_bfloat16*)h, router, correction, ids, weights, T, W, N, n_groups, keep, top);
+    else
+        fwb::pdl(moe_route_kernel<float>, blocks, 128, smem, stream)((const float*)h, router, correction, ids,
+                                                                      weights, T, W, N, n_groups, keep, top);
+    return fwb_launch_status();
+}
+
+// The number of row tiles the products' grids must allow for `pairs` (token, expert) pairs.
+FWB_API int fwb_moe_max_tiles(int pairs, int E) { return (pairs + TM - 1) / TM + E; }
+
+// ids: [A]; offsets: [E + 1]; row_token, pair_row: [A]; tiles: [1 + 2 fwb_moe_max_tiles(A, E)].
+FWB_API int fwb_moe_sort(const int* ids, int A, int top, int E, int* offsets, int* row_token, int* pair_row,
+                         int* tiles, cudaStream_t stream) {
+    if (A <= 0) return FWB_OK;
+    if (!ids || !offsets || !row_token || !pair_row || !tiles || top <= 0 || E < 0) return FWB_BAD_ARGUMENT;
+    if (E > 4096) return FWB_TOO_LARGE;
+    fwb::pdl(moe_sort_kernel, 1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream)(ids, A, top, E, offsets,
+                                                                                  row_token, pair_row, tiles);
+    return fwb_launch_status();
+}
+
+// form 1: x [T][K] (rows gathered by row_token), w [E][2N][K], out [A][N] in the dtype of x.
+// form 0: x [A][K] sorted rows, w [E][N][K], out [A][N] fp32.
+// x and w are both fp32 or both bf16.  max_tiles: fwb_moe_max_tiles of the step.
+FWB_API int fwb_moe_gemm(const void* x, const void* w, int bf16, void* out, const int* offsets,
+                         const int* row_token, const int* tiles, int max_tiles, int N, int K, int form, int act,
+                         cudaStream_t stream) {
+    if (max_tiles <= 0) return FWB_OK;
+    if (!x || !w || !out || !offsets || !row_token || !tiles || N <= 0 || K <= 0 || form < 0 || form > 1 ||
+        act < 0 || act > 1)
+        return FWB_BAD_ARGUMENT;
+    if (max_tiles > 65535) return FWB_TOO_LARGE;
+    const dim3 grid((N + TN - 1) / TN, max_tiles);
+    using bf = __nv_bfloat16;
+    if (form == 1 && bf16)
+        fwb::pdl(moe_gemm_kernel<bf, bf, bf, 1>, grid, 256, 0, stream)((const bf*)x, (const bf*)w, (bf*)out, offsets,
+                                                                       row_token, tiles, N, K, act);
+    else if (form == 1)
+        fwb::pdl(moe_gemm_kernel<float, float, float, 1>, grid, 256, 0, stream)(
+            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act);
+    else if (bf16)
+        fwb::pdl(moe_gemm_kernel<bf, bf, float, 0>, grid, 256, 0, stream)((const bf*)x, (const bf*)w, (float*)out,
+                                                                          offsets, row_token, tiles, N, K, act);
+    else
+        fwb::pdl(moe_gemm_kernel<float, float, float, 0>, grid, 256, 0, stream)(
+            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act);
+    return fwb_launch_status();
+}
+
+// y: [A][W] fp32 sorted rows; h: [T][W]; out: [T][W] fp32.
+FWB_API int fwb_moe_combine(const float* y, const void* h, int h_bf16, const int* pair_row, const int* ids,
+                            const float* weights, float* out, int T, int W, int top, int E, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!y || !h || !pair_row || !ids || !weights || !out || W <= 0 || top <= 0) return FWB_BAD_ARGUMENT;
+    if (h_bf16)
+        fwb::pdl(moe_combine_kernel<__nv_bfloat16>, T, 256, 0, stream)(y, (const __nv_bfloat16*)h, pair_row, ids,
+                                                                       weights, out, W, top, E);
+    else
+        fwb::pdl(moe_combine_kernel<float>, T, 256, 0, stream)(y, (const float*)h, pair_row, ids, weights, out, W,
+                                                               top, E);
+    return fwb_launch_status();
+}

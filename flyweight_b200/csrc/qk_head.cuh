@@ -44,7 +44,7 @@ __device__ __forceinline__ void head_norm_rope8(float (&v)[8], bool valid, int k
     for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
     float total = 0.0f;
     for (int j = 0; j < G; ++j) total += __shfl_sync(0xffffffffu, ss, (sub * G + j) & 31);
-    if (use_norm && !is_v) {
+    if (use_norm == 1 && !is_v) {
         const float inv = rsqrtf(total / (float)hd + eps);
         const float* w = (is_q ? wq : wk) + gl * 8;
         if (valid) {
@@ -55,8 +55,10 @@ __device__ __forceinline__ void head_norm_rope8(float (&v)[8], bool valid, int k
     float other[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, v[i], partner);
-    if (!valid) return;
-    if (!is_v && gl < rot_lanes && pairing) {
+    if (!valid && use_norm != 2) return;
+    if (!valid) {
+        // (mode 2 needs every lane for its shuffles below; a lane without a head holds zeros)
+    } else if (!is_v && gl < rot_lanes && pairing) {
         // interleaved pairs lie side by side in this lane's eight channels
         const float2* c = cs + gl * 4;
 #pragma unroll
@@ -73,6 +75,20 @@ __device__ __forceinline__ void head_norm_rope8(float (&v)[8], bool valid, int k
         for (int i = 0; i < 8; ++i) {
             const float2 a = c[i];
             v[i] = low ? v[i] * a.x - other[i] * a.y : v[i] * a.x + other[i] * a.y;
+        }
+    }
+    if (use_norm == 2) {
+        // mode 2: the head is brought to unit root mean square after the rotation, without a weight
+        // (every lane of the warp takes part in the shuffles; `hd` is the count the mean is taken over)
+        float s2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s2 = fmaf(v[i], v[i], s2);
+        float all = 0.0f;
+        for (int j = 0; j < G; ++j) all += __shfl_sync(0xffffffffu, s2, (sub * G + j) & 31);
+        if (!is_v) {
+            const float inv = rsqrtf(all / (float)hd + eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= inv;
         }
     }
 }

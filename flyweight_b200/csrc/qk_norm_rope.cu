@@ -28,7 +28,7 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
                     const int* __restrict__ positions, const int* __restrict__ tok_seg,
                     const int* __restrict__ block_table, int max_pages, int page_size,
                     TQ* __restrict__ q_out, TC* __restrict__ k_pool, TC* __restrict__ v_pool, int nh,
-                    int nkv, int hd, int rot, float eps, int use_norm, int pairing) {
+                    int nkv, int hd, int rot, float eps, int use_norm, int pairing, int norm_dim) {
     fwb::pdl_entry();
     extern __shared__ float smem[];
     const int t = blockIdx.x;
@@ -61,33 +61,66 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
             ss += v * v;
         }
         ss = warp_sum(ss);
-        const float inv = use_norm ? rsqrtf(ss / (float)hd + eps) : 1.0f;
+        const float inv = use_norm ? rsqrtf(ss / (float)norm_dim + eps) : 1.0f;
         __syncwarp();
         const int half = rot / 2;
+        if (use_norm == 2) {
+            // the rotation first, then the head brought to unit root mean square (no weight): the
+            // turned head goes back into the buffer, its squares are summed again, then the store
+            float a2[MAX_HD / 64], b2[MAX_HD / 64];
+            int n = 0;
+            for (int i = lane; i < half; i += 32, ++n) {
+                const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+                const float2 c = cs[i];
+                a2[n] = buf[ia] * c.x - buf[ib] * c.y;
+                b2[n] = buf[ib] * c.x + buf[ia] * c.y;
+            }
+            __syncwarp();
+            n = 0;
+            for (int i = lane; i < half; i += 32, ++n) {
+                const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+                buf[ia] = a2[n];
+                buf[ib] = b2[n];
+            }
+            __syncwarp();
+            float s2 = 0.0f;
+            for (int i = lane; i < hd; i += 32) s2 += buf[i] * buf[i];
+            s2 = warp_sum(s2);
+            const float inv2 = rsqrtf(s2 / (float)norm_dim + eps);
+            if (is_q) {
+                TQ* dst = q_out + ((size_t)t * nh + h) * hd;
+                for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TQ>(buf[i] * inv2);
+            } else {
+                TC* dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;
+                for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TC>(buf[i] * inv2);
+            }
+            __syncwarp();
+            continue;
+        }
         if (is_q) {
             TQ* dst = q_out + ((size_t)t * nh + h) * hd;
             for (int i = lane; i < half; i += 32) {
                 const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
-                const float a = use_norm ? (buf[ia] * inv) * w[ia] : buf[ia];
-                const float b = use_norm ? (buf[ib] * inv) * w[ib] : buf[ib];
+                const float a = use_norm == 1 ? (buf[ia] * inv) * w[ia] : buf[ia];
+                const float b = use_norm == 1 ? (buf[ib] * inv) * w[ib] : buf[ib];
                 const float2 c = cs[i];
                 dst[ia] = from_f32<TQ>(a * c.x - b * c.y);
                 dst[ib] = from_f32<TQ>(b * c.x + a * c.y);
             }
             for (int i = rot + lane; i < hd; i += 32)
-                dst[i] = from_f32<TQ>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
+                dst[i] = from_f32<TQ>(use_norm == 1 ? (buf[i] * inv) * w[i] : buf[i]);
         } else {
             TC* dst = k_pool + cache_base + (size_t)(h - nh) * page_size * hd;
             for (int i = lane; i < half; i += 32) {
                 const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
-                const float a = use_norm ? (buf[ia] * inv) * w[ia] : buf[ia];
-                const float b = use_norm ? (buf[ib] * inv) * w[ib] : buf[ib];
+                const float a = use_norm == 1 ? (buf[ia] * inv) * w[ia] : buf[ia];
+                const float b = use_norm == 1 ? (buf[ib] * inv) * w[ib] : buf[ib];
                 const float2 c = cs[i];
                 dst[ia] = from_f32<TC>(a * c.x - b * c.y);
                 dst[ib] = from_f32<TC>(b * c.x + a * c.y);
             }
             for (int i = rot + lane; i < hd; i += 32)
-                dst[i] = from_f32<TC>(use_norm ? (buf[i] * inv) * w[i] : buf[i]);
+                dst[i] = from_f32<TC>(use_norm == 1 ? (buf[i] * inv) * w[i] : buf[i]);
         }
         __syncwarp();
     }
@@ -104,7 +137,7 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
                            const int* __restrict__ block_table, int max_pages, int page_size,
                            __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
                            __nv_bfloat16* __restrict__ v_pool, int nh, int nkv, int hd, int rot, float eps,
-                           int use_norm, int pairing) {
+                           int use_norm, int pairing, int norm_dim) {
     fwb::pdl_entry();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,7 +164,7 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
             for (int i = 0; i < 8; ++i) v[i] = 0.0f;
         }
         const bool is_v = h >= nh + nkv, is_q = h < nh;
-        head_norm_rope8(v, valid, is_q ? 0 : (is_v ? 2 : 1), sub, gl, G, hd, rot, pairing, use_norm, eps, wq, wk, cs);
+        head_norm_rope8(v, valid, is_q ? 0 : (is_v ? 2 : 1), sub, gl, G, norm_dim, rot, pairing, use_norm, eps, wq, wk, cs);
         if (!valid) continue;
         __nv_bfloat16* dst;
         if (is_q) dst = q_out + ((size_t)t * nh + h) * hd;
@@ -148,17 +181,24 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
 // pairing: 0 half-split (i, i+rot/2), 1 interleaved (2i, 2i+1).
 // block_table: [S][max_pages] page ids.  q_out: [T][nh*hd].  k_pool, v_pool:
 // [pages][nkv][page_size][hd].  Dtype flags: 0 fp32, 1 bf16.
-FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, const float* wk,
-                             const void* table, const int* positions, const int* tok_seg,
-                             const int* block_table, int max_pages, int page_size, void* q_out,
-                             int q_bf16, void* k_pool, void* v_pool, int cache_bf16, int T, int nh,
-                             int nkv, int hd, int rot, float eps, int use_norm, int pairing,
-                             cudaStream_t stream) {
+//
+// use_norm: 0 none; 1 RMS norm with the weights wq / wk, then the rotation; 2 the rotation first, then
+// every head of q and k brought to unit root mean square, without a weight.  norm_dim: the number of
+// channels the mean of squares is taken over (0: hd; fewer when the heads' last channels are zero
+// padding).
+FWB_API int fwb_qk_norm_rope_ordered(const void* qkv, int in_bf16, const float* wq, const float* wk,
+                                     const void* table, const int* positions, const int* tok_seg,
+                                     const int* block_table, int max_pages, int page_size, void* q_out,
+                                     int q_bf16, void* k_pool, void* v_pool, int cache_bf16, int T, int nh,
+                                     int nkv, int hd, int rot, float eps, int use_norm, int pairing,
+                                     int norm_dim, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
+    if (use_norm < 0 || use_norm > 2 || norm_dim < 0 || norm_dim > hd) return FWB_BAD_ARGUMENT;
+    if (norm_dim == 0) norm_dim = hd;
     if (!qkv || !table || !positions || !q_out || nh <= 0 || nkv < 0) return FWB_BAD_ARGUMENT;
     if (nkv > 0 && (!tok_seg || !block_table || !k_pool || !v_pool || page_size <= 0 || max_pages <= 0))
         return FWB_BAD_ARGUMENT;
-    if (use_norm && (!wq || (nkv > 0 && !wk))) return FWB_BAD_ARGUMENT;
+    if (use_norm == 1 && (!wq || (nkv > 0 && !wk))) return FWB_BAD_ARGUMENT;
     if (hd <= 0 || hd > MAX_HD || (hd & 1) || rot < 0 || rot > hd || (rot & 1)) return FWB_UNSUPPORTED;
     if (pairing != 0 && pairing != 1) return FWB_UNSUPPORTED;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
@@ -170,7 +210,7 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
 #define FWB_QK(TI, TQ, TC)                                                                        \
     fwb::pdl(qk_norm_rope_kernel<TI, TQ, TC>, grid, WARPS * 32, smem, stream)(                             \
         (const TI*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table, max_pages, \
-        page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm, pairing)
+        page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm, pairing, norm_dim)
     const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
     if (key == 7 && (hd & 7) == 0 && hd <= 256 && (rot & 15) == 0 && aligned) {
@@ -179,7 +219,7 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
         fwb::pdl(qk_norm_rope_bf16x8_kernel, vgrid, WARPS * 32, 0, stream)(
             (const __nv_bfloat16*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
             max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
-            nkv, hd, rot, eps, use_norm, pairing);
+            nkv, hd, rot, eps, use_norm, pairing, norm_dim);
         return fwb_launch_status();
     }
     switch (key) {
@@ -190,4 +230,15 @@ FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, cons
     }
 #undef FWB_QK
     return fwb_launch_status();
+}
+
+FWB_API int fwb_qk_norm_rope(const void* qkv, int in_bf16, const float* wq, const float* wk,
+                             const void* table, const int* positions, const int* tok_seg,
+                             const int* block_table, int max_pages, int page_size, void* q_out,
+                             int q_bf16, void* k_pool, void* v_pool, int cache_bf16, int T, int nh,
+                             int nkv, int hd, int rot, float eps, int use_norm, int pairing,
+                             cudaStream_t stream) {
+    return fwb_qk_norm_rope_ordered(qkv, in_bf16, wq, wk, table, positions, tok_seg, block_table, max_pages,
+                                    page_size, q_out, q_bf16, k_pool, v_pool, cache_bf16, T, nh, nkv, hd, rot,
+                                    eps, use_norm ? 1 : 0, pairing, 0, stream);
 }

@@ -214,6 +214,15 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 // that.  For g << 0, e^-g overflows to +inf and the quotient is -0, the right limit.
 __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
+// The activation on the gate of a gated feed-forward, chosen at run time (one uniform branch per
+// epilogue): 0 = silu, 1 = the tanh form of gelu, 0.5 g (1 + tanh(c (g + 0.044715 g^3))) with
+// c = sqrt(2/pi), which is g * sigmoid(2 c (g + 0.044715 g^3)): the same quotient as silu.
+constexpr int GATE_SILU = 0, GATE_GELU_TANH = 1;
+__device__ __forceinline__ float gate_act_fast(int act, float g) {
+    const float z = act == GATE_GELU_TANH ? 1.5957691216057308f * fmaf(0.044715f * g, g * g, g) : g;
+    return __fdividef(g, 1.0f + __expf(-z));
+}
+
 // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     uint64_t d = 0;

@@ -1,0 +1,60 @@
+"""Python faces of the mixture-of-experts kernels (``csrc/moe.cu``): router, sorting of the
+(token, expert) pairs, the experts' products over the sorted rows, the weighted sum."""
+from __future__ import annotations
+
+import torch
+
+from . import lib
+from .lib import KernelError, c_float, check_tensor, is_bf16, ptr, stream
+from .ops import GATE_ACTIVATIONS
+
+
+def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int):
+    """ids int32 [T][top] and weights fp32 [T][top]: softmax scores over all router outputs; the choice
+    on score + correction inside the ``keep`` best of ``n_groups`` runs of neighbours; the weights are
+    the chosen outputs' plain scores."""
+    check_tensor("router input", h)
+    T, W = h.shape
+    N = router.shape[0]
+    check_tensor("router", router, torch.float32, (N, W))
+    check_tensor("router correction", correction, torch.float32, (N,))
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    lib.call("fwb_moe_route", ptr(h), is_bf16(h), ptr(router), ptr(correction), ptr(ids), ptr(weights), T, W, N,
+             int(n_groups), int(keep), int(top), stream())
+    return ids, weights
+
+
+def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                    w_down: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """``sum_slot weights * expert(h)`` as fp32 [T][W].  ``w_gate_up``: [E][2F][W] (gate rows, then up
+    rows), ``w_down``: [E][W][F], both in the dtype of ``h``.  Router outputs from E on are identity
+    experts: they pass ``h`` itself on."""
+    check_tensor("expert input", h)
+    T, W = h.shape
+    top = ids.shape[1]
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    check_tensor("expert gate|up", w_gate_up, h.dtype, (E, 2 * F, W))
+    check_tensor("expert down", w_down, h.dtype, (E, W, F))
+    check_tensor("expert ids", ids, torch.int32, (T, top))
+    check_tensor("expert weights", weights, torch.float32, (T, top))
+    act = GATE_ACTIVATIONS[activation]
+    A = T * top
+    max_tiles = lib.library().fwb_moe_max_tiles(A, E)
+    dev = h.device
+    meta = torch.empty(E + 1 + 2 * A + 1 + 2 * max_tiles, dtype=torch.int32, device=dev)
+    offsets, row_token = meta[:E + 1], meta[E + 1:E + 1 + A]
+    pair_row, tiles = meta[E + 1 + A:E + 1 + 2 * A], meta[E + 1 + 2 * A:]
+    lib.call("fwb_moe_sort", ptr(ids), A, top, E, ptr(offsets), ptr(row_token), ptr(pair_row), ptr(tiles), stream())
+    bf16 = is_bf16(h)
+    a = torch.empty((A, F), dtype=h.dtype, device=dev)
+    lib.call("fwb_moe_gemm", ptr(h), ptr(w_gate_up), bf16, ptr(a), ptr(offsets), ptr(row_token), ptr(tiles),
+             max_tiles, F, W, 1, act, stream())
+    y = torch.empty((A, W), dtype=torch.float32, device=dev)
+    lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
+             max_tiles, W, F, 0, 0, stream())
+    out = torch.empty((T, W), dtype=torch.float32, device=dev)
+    lib.call("fwb_moe_combine", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(out), T, W, top,
+             E, stream())
+    return out

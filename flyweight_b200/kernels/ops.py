@@ -69,6 +69,26 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
+def rmsnorm_add_(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                 next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                 next_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``x += weight * y / sqrt(mean(y^2) + eps)`` per row, in place and in fp32: a norm on a
+    sublayer's output with the residual sum behind it.  With ``next_weight`` the same pass also
+    returns ``next_weight * x / sqrt(mean(x^2) + next_eps)`` of the new rows in ``next_dtype``: the norm
+    in front of the next sublayer."""
+    check_tensor("residual", x, torch.float32)
+    check_tensor("sublayer output", y, torch.float32, x.shape)
+    H = x.shape[-1]
+    check_tensor("norm weight", weight, torch.float32, (H,))
+    out = None
+    if next_weight is not None:
+        check_tensor("next norm weight", next_weight, torch.float32, (H,))
+        out = torch.empty(x.shape, dtype=next_dtype or torch.float32, device=x.device)
+    lib.call("fwb_rmsnorm_add", ptr(x), ptr(y), ptr(weight), c_float(eps), ptr(next_weight), c_float(next_eps),
+             ptr(out), is_bf16(out) if out is not None else 0, x.numel() // H, H, stream())
+    return out
+
+
 def add_(x: torch.Tensor, delta: torch.Tensor) -> None:
     check_tensor("residual", x, torch.float32)
     check_tensor("delta", delta, torch.float32, x.shape)
@@ -164,6 +184,25 @@ def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gate_act_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` for ``gate_up`` = [T][gate(F) | up(F)]; ``activation``: "silu" or "gelu_tanh"
+    (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))))."""
+    check_tensor("gate|up", gate_up)
+    T, F2 = gate_up.shape
+    if F2 % 2:
+        raise KernelError("gate|up needs an even number of columns")
+    try:
+        act = GATE_ACTIVATIONS[activation]
+    except KeyError:
+        raise KernelError(f"unknown gate activation {activation!r}; known: " + ", ".join(GATE_ACTIVATIONS)) from None
+    out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    lib.call("fwb_gate_act_mul", ptr(gate_up), is_bf16(gate_up), ptr(out), is_bf16(out), T, F2 // 2, act, stream())
+    return out
+
+
 # ------------------------------------------------------------------ gated short convolution
 def shortconv(p: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
               state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
@@ -201,9 +240,14 @@ def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Opti
                  table: torch.Tensor, positions: torch.Tensor, tok_seg: torch.Tensor,
                  block_table: Optional[torch.Tensor], k_pool: Optional[torch.Tensor],
                  v_pool: Optional[torch.Tensor], n_heads: int, n_kv_in: int, head_dim: int,
-                 rotary_dim: int, eps: float, q_dtype: torch.dtype, pairing: str = "half_split"
-                 ) -> torch.Tensor:
+                 rotary_dim: int, eps: float, q_dtype: torch.dtype, pairing: str = "half_split",
+                 unit_rms_after: bool = False, norm_dim: int = 0) -> torch.Tensor:
     """Per-head RMSNorm + RoPE of q and k, k/v written to their pages; returns q [T][nh*hd].
+
+    ``unit_rms_after``: instead of the weighted norm in front of the rotation, every head of q and k
+    is brought to unit root mean square *behind* it, without a weight (``q_norm``/``k_norm`` are not
+    read).  ``norm_dim``: over how many channels the mean of squares is taken (0: all ``head_dim``; fewer
+    when the last channels of every head are zero padding).
 
     ``n_kv_in`` is the number of KV heads present in ``qkv`` (0: queries only).
     ``table`` is [max_pos][rotary_dim/2][2] fp32 (cos, sin); pair i turns by entry i.
@@ -221,11 +265,13 @@ def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Opti
     check_tensor("rope table", table, torch.float32)
     if table.dim() != 3 or table.shape[1] != max(1, rotary_dim // 2) or table.shape[2] != 2:
         raise KernelError("rope table must be [positions][rotary_dim/2][2]")
-    use_norm = 1 if q_norm is not None else 0
-    if use_norm:
+    use_norm = 2 if unit_rms_after else (1 if q_norm is not None else 0)
+    if use_norm == 1:
         check_tensor("q norm weight", q_norm, torch.float32, (head_dim,))
         if n_kv_in:
             check_tensor("k norm weight", k_norm, torch.float32, (head_dim,))
+    if not 0 <= norm_dim <= head_dim:
+        raise KernelError(f"the norm of a head of {head_dim} channels cannot go over {norm_dim}")
     _i32("positions", positions, T)
     _i32("tok_seg", tok_seg, T)
     max_pages = page_size = 0
@@ -241,10 +287,11 @@ def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Opti
     q_out = torch.empty((T, n_heads * head_dim), dtype=q_dtype, device=qkv.device)
     if n_kv_in == 0:
         cache_bf16 = is_bf16(q_out)
-    lib.call("fwb_qk_norm_rope", ptr(qkv), is_bf16(qkv), ptr(q_norm), ptr(k_norm), ptr(table),
+    lib.call("fwb_qk_norm_rope_ordered", ptr(qkv), is_bf16(qkv), ptr(q_norm if use_norm == 1 else None),
+             ptr(k_norm if use_norm == 1 else None), ptr(table),
              ptr(positions), ptr(tok_seg), ptr(block_table), max_pages, page_size, ptr(q_out),
              is_bf16(q_out), ptr(k_pool), ptr(v_pool), cache_bf16, T, n_heads, n_kv_in, head_dim,
-             rotary_dim, c_float(eps), use_norm, pairing_code, stream())
+             rotary_dim, c_float(eps), use_norm, pairing_code, int(norm_dim), stream())
     return q_out
 
 

@@ -11,6 +11,14 @@ from . import lib
 from .lib import KernelError, check_tensor, ptr, stream
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
+# the activation on the gate rides in the bits above the epilogue code (0: silu)
+GATE_ACT_SHIFT = 8
+
+
+def _gated_epilogue(activation: str) -> int:
+    from .ops import GATE_ACTIVATIONS
+    return EPI_SWIGLU_BF16 | (GATE_ACTIVATIONS[activation] << GATE_ACT_SHIFT)
+
 SM_COUNT = 148
 _enabled = True
 
@@ -231,7 +239,7 @@ def swiglu_accepts(x, w_gate_up) -> bool:
     return accepts(x, w_gate_up, torch.bfloat16)
 
 
-def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.Tensor:
+def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0, activation="silu") -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` as bf16, for ``w_gate_up`` = [gate rows | up rows]:
     both products accumulate side by side in tensor memory and never reach global memory."""
     check_tensor("swiglu input", x, torch.bfloat16)
@@ -241,6 +249,7 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
     F = F2 // 2
     if w_gate_up.shape[1] != K or F * 2 != F2:
         raise KernelError("swiglu: weight must be [2F][K]")
+    gated = _gated_epilogue(activation)
     out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
     if M <= 64 and (F, K, 2) in TUNED and _forced_splits is None:
         tuned = TUNED[(F, K, 2)]
@@ -264,12 +273,12 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.
         # as many CTAs of half the length, which fit one wave and start as the first launch drains.
         first = cut * 128
         lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, first, K, F2, F,
-                 EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream(), tag=f"swiglu {F}x{K} first")
+                 gated, F, 1, 0, 256, -1, stream(), tag=f"swiglu {F}x{K} first")
         lib.call("fwb_gemm_tcgen05", ptr(x), _offset(w_gate_up, first * K), _offset(out, first), ptr(None), M,
-                 F - first, K, F2 - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, stream(), tag=f"swiglu {F}x{K} rest")
+                 F - first, K, F2 - first, F, gated, F, 1, 0, 128, -1, stream(), tag=f"swiglu {F}x{K} rest")
         return out
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
-             EPI_SWIGLU_BF16, F, splits, stages, tile_tokens, -1, stream(), tag=f"swiglu {F}x{K} splits {splits}")
+             gated, F, splits, stages, tile_tokens, -1, stream(), tag=f"swiglu {F}x{K} splits {splits}")
     return out
 
 
@@ -358,7 +367,8 @@ def gemm_normed(x_res, norm_weight, eps, w, out_dtype, rows=None, n_rows=None, s
     return out
 
 
-def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stages=0, tile_tokens=0) -> torch.Tensor:
+def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stages=0, tile_tokens=0,
+                          activation="silu") -> torch.Tensor:
     """``silu(n @ gate.T) * (n @ up.T)`` with n = rmsnorm(x_res), in one kernel."""
     check_tensor("residual", x_res, torch.float32)
     check_tensor("norm weight", norm_weight, torch.float32)
@@ -369,13 +379,14 @@ def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stage
     F = F2 // 2
     if w_gate_up.shape[1] != K or F * 2 != F2 or norm_weight.numel() != K:
         raise KernelError("swiglu: weight must be [2F][K] and the norm weight [K]")
+    gated = _gated_epilogue(activation)
     out = torch.empty((M, F), dtype=torch.bfloat16, device=x_res.device)
     if splits is None:
         splits = _forced_splits if _forced_splits is not None else _splits_for(M, F, K, 2)
     stages = stages or _ring_depth(M, F, splits, 2)
     tile_tokens = tile_tokens or _decode_tile(M, F)
     lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(None), lib.c_float(eps),
-             ptr(w_gate_up), ptr(out), M, F, K, F2, F, EPI_SWIGLU_BF16, F, splits, stages, tile_tokens,
+             ptr(w_gate_up), ptr(out), M, F, K, F2, F, gated, F, splits, stages, tile_tokens,
              stream(), tag=f"normed swiglu {F}x{K} splits {splits}")
     return out
 

@@ -4,8 +4,8 @@ from .base import (Arrangement, Embedding, FeedForward, FixedState, Mixer, Norm,
                    build_mixer, build_norm, build_position, register_arrangement,
                    register_embedding, register_feed_forward, register_mixer, register_norm,
                    register_position, register_shift)
-from . import (attention, block, embedding, latent_attention, norm, outnorm_block, rope, shortconv,  # noqa: F401
-               swiglu, token_shift)  # noqa: F401  (register the parts)
+from . import (attention, block, delta_rule, embedding, latent_attention, moe, norm, outnorm_block, rope,  # noqa: F401
+               sandwich_block, shortconv, swiglu, token_shift)  # noqa: F401  (register the parts)
 
 __all__ = [
     "Arrangement", "Embedding", "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "Part",

@@ -186,16 +186,20 @@ class PositionEncoding(Part):
                        else torch.zeros((1, 1, 2), dtype=torch.float32, device=device))
 
     def encode(self, ctx, qkv, *, n_heads: int, n_kv_in: int, head_dim: int, q_norm, k_norm,
-               eps: float, cache, block_table):
+               eps: float, cache, block_table, unit_rms_after: bool = False, norm_dim: int = 0):
         """qkv: [T][(n_heads + 2 n_kv_in) head_dim] in the activation dtype (``n_kv_in`` 0: queries
-        only, for a mixer that reads another execution's cache).  Returns q [T][n_heads head_dim]."""
+        only, for a mixer that reads another execution's cache).  Returns q [T][n_heads head_dim].
+        ``unit_rms_after`` (only handed over when set): no weighted norm in front of the rotation;
+        every head of q and k is brought to unit root mean square behind it, the mean taken over the
+        head's first ``norm_dim`` channels (the rest is zero padding)."""
         from ..kernels import ops
         batch = ctx.batch
         return ops.qk_norm_rope(
             qkv, q_norm, k_norm, self._table, batch.positions, batch.tok_seg,
             block_table if n_kv_in else None, cache.k_pool if n_kv_in else None,
             cache.v_pool if n_kv_in else None, n_heads, n_kv_in, head_dim, self.rotary_dim,
-            float(eps or 0.0), ctx.precision.act_dtype, pairing=self.pairing)
+            float(eps or 0.0), ctx.precision.act_dtype, pairing=self.pairing,
+            unit_rms_after=unit_rms_after, norm_dim=norm_dim)
 
     def rotation(self):
         """(table, rotary_dim, pairing) for a mixer that can do the default ``encode`` inside a kernel

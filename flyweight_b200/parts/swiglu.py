@@ -12,7 +12,8 @@ from .base import FeedForward, Precision, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, ffn_dim.  tensors: gate [F][H], up [F][H], down [H][F]."""
+    """params: hidden_size, ffn_dim, activation ("silu", the default, or "gelu_tanh": what acts on the
+    gate).  tensors: gate [F][H], up [F][H], down [H][F]."""
     graph_safe = True
     takes_deferred_norm = True
     adds_residual = True
@@ -21,6 +22,10 @@ class SwiGLU(FeedForward):
         super().__init__(spec)
         self.hidden = int(self.params["hidden_size"])
         self.ffn_dim = int(self.params["ffn_dim"])
+        self.activation = str(self.params.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"unknown gate activation {self.activation!r}; known: "
+                             + ", ".join(ops.GATE_ACTIVATIONS))
         self.w_gate_up = self.w_down = None
 
     def declare(self):
@@ -50,20 +55,27 @@ class SwiGLU(FeedForward):
             if h.kind == "rmsnorm" and tensorcore.normed_accepts(h.n_rows, self.hidden, self.w_gate_up, 2,
                                                                   self.ffn_dim):
                 # the norm, both products and silu(g)*u in one kernel
-                a = tensorcore.swiglu_gate_up_normed(h.x, h.weight, h.eps, self.w_gate_up)
+                a = tensorcore.swiglu_gate_up_normed(h.x, h.weight, h.eps, self.w_gate_up,
+                                                     activation=self.activation)
                 return ops.linear_into_residual(a, self.w_down, residual)
             h = h.materialize(act)
         if tensorcore.swiglu_accepts(h, self.w_gate_up):
             # gate and up accumulate side by side in tensor memory; silu(g)*u is the epilogue
-            a = tensorcore.swiglu_gate_up(h, self.w_gate_up)
+            a = tensorcore.swiglu_gate_up(h, self.w_gate_up, activation=self.activation)
         else:
             gate_up = ops.linear(h, self.w_gate_up, act)
-            a = ops.silu_mul(gate_up, act)
+            a = ops.gate_act_mul(gate_up, act, self.activation)
         return ops.linear_into_residual(a, self.w_down, residual)
+
+    def _silu_only(self):
+        if self.activation != "silu":
+            from ..engine.plan import NotPlannable
+            raise NotPlannable(f"the native plan has the gated product with silu only, not {self.activation!r}")
 
     def plan_stream(self, builder, h, out):
         """For an arrangement without a norm in front: gate|up with silu(g)*u from the buffer ``h``, down
         into ``out`` (fp32)."""
+        self._silu_only()
         a = builder.tokens(self.ffn_dim, builder.act_dtype)
         builder.swiglu(h, self.w_gate_up, a, "gate|up")
         builder.linear(a, self.w_down, out, "down")
@@ -72,6 +84,7 @@ class SwiGLU(FeedForward):
     def plan(self, builder, norm):
         """Norm, gate|up with silu(g)*u, down with the residual sum, for the native step plan."""
         from ..engine.plan import EPI_SWIGLU
+        self._silu_only()
         a = builder.tokens(self.ffn_dim, builder.act_dtype)
         builder.norm_linear(norm, self.w_gate_up, EPI_SWIGLU, a, "gate|up")
         builder.linear_residual(a, self.w_down, "down")

@@ -114,5 +114,67 @@ KEMITAR_D = {
 TINY.update({"KA": KEMITAR_A, "KB": KEMITAR_B, "KC": KEMITAR_C, "KD": KEMITAR_D})
 
 
+def _chunk_attention(heads, kv_heads, dim, vdim, chunk, base, rot_dims, scale, kv_from=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale,
+             "rot": {"base": base, "dims": rot_dims}, "mask": {"size": chunk}}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "attention", "mixer": mixer}
+
+
+def _delta(heads, kv_heads, dim, vdim, conv):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def _experts(ff, experts, identity, top, groups=None, keep=None):
+    router = {"experts": experts, "identity": identity, "top": top}
+    if groups is not None:
+        router["groups"] = {"count": groups, "keep": keep}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": router}
+
+
+# Three tiny Diforax configurations that differ in every size and option: the order of the layers (a
+# delta rule first, attention first), head counts and groups (1 to 4 query heads per key head), query
+# and value sizes that differ both ways, partial and full rotation, chunks shorter than, equal to and
+# longer than a page, a layer that reads another's keys under a chunk of its own, layers without a
+# feed-forward, taps from 2 to 4, state sizes that fill no warp, routers with and without identity
+# experts and groups, top 1.
+DIFORAX_A = {
+    "architecture": "Diforax", "vocab": 211, "width": 80, "norm": {"eps": 1e-5},
+    "layers": [
+        {**_delta(4, 2, 16, 24, 4), "mlp": _experts(48, 6, 2, 3, groups=4, keep=2)},
+        {**_chunk_attention(6, 3, 32, 16, 48, 10000.0, 16, 0.2), "mlp": _dense(144)},
+        {**_chunk_attention(6, 3, 32, 16, 37, 10000.0, 16, 0.3, kv_from=1), "mlp": None},
+        {**_delta(2, 2, 8, 8, 2), "mlp": _dense(112)},
+    ],
+}
+
+DIFORAX_B = {
+    "architecture": "Diforax", "vocab": 130, "width": 96, "norm": {"eps": 1e-6},
+    "layers": [
+        {**_chunk_attention(4, 1, 16, 48, 64, 500.0, 16, 0.25), "mlp": _experts(40, 5, 0, 1)},
+        {**_delta(3, 1, 40, 20, 3), "mlp": None},
+        {**_chunk_attention(2, 2, 64, 64, 100, 1000000.0, 32, 0.11), "mlp": _experts(24, 3, 3, 4, groups=3, keep=2)},
+    ],
+}
+
+# Head sizes and group widths that the tensor-core attention kernels take, so that the bfloat16 path
+# runs them: 128 channels, four query heads per key head.
+DIFORAX_C = {
+    "architecture": "Diforax", "vocab": 300, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {**_chunk_attention(8, 2, 128, 128, 130, 10000.0, 64, 0.09), "mlp": _dense(256)},
+        {**_delta(4, 2, 64, 128, 4), "mlp": _experts(64, 8, 0, 2, groups=2, keep=1)},
+        {**_chunk_attention(8, 2, 128, 128, 70, 10000.0, 64, 0.07, kv_from=0), "mlp": _dense(192)},
+    ],
+}
+
+TINY.update({"DA": DIFORAX_A, "DB": DIFORAX_B, "DC": DIFORAX_C})
+
+
 def vocab_of(config: dict) -> int:
     return int(config.get("vocab_size", config.get("vocab")))
