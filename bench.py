@@ -61,11 +61,42 @@ def kemitar_like(lfm2: dict, ff: int) -> dict:
             "layers": layers}
 
 
-# Kemitar beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what LFM2's rule
-# makes of ``intermediate_size`` at these sizes.
+def diforax_like(lfm2: dict, ff: int) -> dict:
+    """A Diforax configuration with the layer sizes of an LFM2 one (width, depth, vocabulary, attention at
+    the same places with the same heads): chunks of 8,192 positions, every second attention layer reading
+    the keys of the attention layer before it, a dense gated feed-forward of LFM2's width behind attention;
+    where LFM2 has a short convolution, a gated delta rule with as many weights (width / 128 heads of 128 x
+    128 state, half as many q/k heads, 4 taps) and routed experts that use as much of the feed-forward per
+    token (30 experts of ff / 8 and 2 identity experts, 8 of 32 chosen inside 2 of 4 groups)."""
+    width, heads, kv = lfm2["hidden_size"], lfm2["num_attention_heads"], lfm2["num_key_value_heads"]
+    layers, last_owner = [], None
+    for index in range(lfm2["num_hidden_layers"]):
+        if index in lfm2["full_attn_idxs"]:
+            mixer = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125,
+                     "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": 8192}}
+            if last_owner is not None:
+                mixer["kv_from"], last_owner = last_owner, None
+            else:
+                last_owner = index
+            layers.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            mixer = {"heads": width // 128, "kv_heads": width // 256, "dim": 128, "vdim": 128, "conv": 4}
+            mlp = {"kind": "moe", "expert": {"ff": ff // 8},
+                   "router": {"experts": 30, "identity": 2, "top": 8, "groups": {"count": 4, "keep": 2}}}
+            layers.append({"type": "delta", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Diforax", "vocab": lfm2["vocab_size"], "width": width, "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+# Kemitar and Diforax beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what
+# LFM2's rule makes of ``intermediate_size`` at these sizes.
 KEMITAR = {"kemitar-350m": ("lfm2-350m", 4608), "kemitar-1.2b": ("lfm2-1.2b", 8192)}
 for _name, (_twin, _ff) in KEMITAR.items():
     MODELS[_name] = kemitar_like(MODELS[_twin], _ff)
+DIFORAX = {"diforax-350m": ("lfm2-350m", 4608), "diforax-1.2b": ("lfm2-1.2b", 8192)}
+for _name, (_twin, _ff) in DIFORAX.items():
+    MODELS[_name] = diforax_like(MODELS[_twin], _ff)
+COMPARE = {**KEMITAR, **DIFORAX}
 
 
 def vocab_of(config: dict) -> int:
@@ -152,6 +183,31 @@ def attention_flops(model, n_tokens: int) -> float:
     """Causal attention of one n-token prompt: QK^T and PV, 2 * n^2 * heads * head_dim a layer
     (4 flops per query-key pair and channel, half of the pairs masked), as the mixers state it."""
     return model.context_flops(n_tokens)
+
+
+def state_bytes_per_request(model) -> int:
+    """Bytes of fixed-size state (recurrent matrices, convolution inputs) one request keeps: a decode
+    step reads and writes all of it."""
+    total = 0
+    for entry in model.spec.schedule:
+        spec = model.layers[entry.layer].state_spec()
+        for member in (spec if isinstance(spec, tuple) else (spec,)):
+            if member is not None and hasattr(member, "shape"):
+                count = 1
+                for extent in member.shape:
+                    count *= int(extent)
+                total += count * member.dtype.itemsize
+    return total
+
+
+def context_seen(model, context: int) -> int:
+    """How many cached positions a decoded token at ``context`` reads at most (a chunked mask cuts it)."""
+    seen = context
+    for layer in model.layers:
+        chunk = getattr(getattr(layer, "mixer", None), "chunk", 0)
+        if chunk:
+            seen = min(seen, context % chunk + 1 if context % chunk else chunk)
+    return seen
 
 
 def kv_bytes_per_token(model) -> int:
@@ -418,18 +474,18 @@ def run_sizes(args) -> int:
 
 
 def run_compare(args) -> int:
-    """``--compare kemitar-350m|kemitar-1.2b``: Kemitar with random weights beside LFM2 at equal layer
+    """``--compare kemitar-350m|kemitar-1.2b|diforax-350m|diforax-1.2b``: the model with random weights beside LFM2 at equal layer
     sizes, both through the same step function -- prompts of 512, 2,048 and 8,192 tokens in one step
     (tokens/s and TFLOP/s of the model's own flop count) and decode steps at batch 1, 8 and 64 over 4,096
     cached tokens (tokens/s, and the bytes a step must read against the measured copy bandwidth).  One
     JSON line per model; the LFM2 line's ffn width is checked to be the one the Kemitar twin was given."""
     import torch
     from flyweight_b200.engine.runtime import Model
-    if args.compare not in KEMITAR:
-        print(json.dumps({"error": f"--compare wants one of {sorted(KEMITAR)}"}))
+    if args.compare not in COMPARE:
+        print(json.dumps({"error": f"--compare wants one of {sorted(COMPARE)}"}))
         return 1
     peaks = read_peaks()
-    twin, ff = KEMITAR[args.compare]
+    twin, ff = COMPARE[args.compare]
     for name in (args.compare, twin):
         config = dict(MODELS[name])
         model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
@@ -438,7 +494,8 @@ def run_compare(args) -> int:
             return 1
         vocab = vocab_of(config)
         line = {"compare": args.compare, "model": name, "parameters": model.parameter_count(),
-                "cache_bytes_per_token": kv_bytes_per_token(model), "of": peaks["source"], "prefill": {}, "decode": {}}
+                "cache_bytes_per_token": kv_bytes_per_token(model),
+                "state_bytes_per_request": state_bytes_per_request(model), "of": peaks["source"], "prefill": {}, "decode": {}}
         for n_tokens in (512, 2048, 8192):
             ms = time_prefill(model, n_tokens, vocab)
             flops = (model_flops_per_token(model) * n_tokens + attention_flops(model, n_tokens)
@@ -449,7 +506,11 @@ def run_compare(args) -> int:
                 "frac": round(flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 3)}
         for batch in (1, 8, 64):
             timed = time_decode(model, batch, CONTEXT, args.steps, args.warmup, vocab)
-            step_bytes = model.weight_bytes(with_embedding_rows=batch) + batch * CONTEXT * kv_bytes_per_token(model)
+            # what a step must move: the weights it touches (of routed experts: those its tokens can
+            # choose), every request's cached keys and values, and its fixed-size state in and out
+            step_bytes = (model.weight_bytes(with_embedding_rows=batch, tokens=batch)
+                          + batch * min(CONTEXT, context_seen(model, CONTEXT)) * kv_bytes_per_token(model)
+                          + 2 * batch * state_bytes_per_request(model))
             line["decode"][f"b{batch}"] = {
                 "ms_per_step": round(timed["ms_per_step"], 4), "tokens_per_s": round(timed["tokens_per_s"]),
                 "gb_per_step": round(step_bytes / 1e9, 3),
@@ -742,7 +803,7 @@ def main() -> int:
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
     parser.add_argument("--compare", default=None, metavar="MODEL",
-                        help="kemitar-350m or kemitar-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
+                        help="kemitar-350m, kemitar-1.2b, diforax-350m or diforax-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
     parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode[@BATCHxCONTEXT]|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()

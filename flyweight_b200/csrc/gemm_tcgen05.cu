@@ -113,6 +113,13 @@ struct Params {
     const float* norm_w;
     const int* norm_rows;
     float norm_eps;
+    // Grouped form (null: off): the rows of X are sorted by group, group g owning rows offsets[g] to
+    // offsets[g + 1] and the rows g * group_w_rows onwards of W.  group_tiles[0] is the number of token
+    // tiles, group_tiles[1 + 2 i] and [2 + 2 i] the group and the first row of tile i; blockIdx.x is the
+    // tile, and a CTA beyond the list's end returns at once.
+    const int* group_tiles;
+    const int* group_offsets;
+    int group_w_rows;
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -236,8 +243,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles are the fast grid dimension: CTAs that run together share weight tiles, and
     // a wave's weights plus all the activations fit the L2 cache
-    const int feat0 = blockIdx.y * (WIDE ? 2 * BM : BM), tok0 = blockIdx.x * BN;
-    const int second_tile_row = WIDE ? feat0 + BM : prm.up_row_offset + feat0;   // accumulator 1's rows of W
+    int tok0 = blockIdx.x * BN, m_end = prm.M, w_shift = 0;
+    if (prm.group_tiles) {
+        // the tile list is the work of an earlier kernel of this step: nothing is read before it is done
+        pdl_wait();
+        if ((int)blockIdx.x >= prm.group_tiles[0]) return;
+        const int group = prm.group_tiles[1 + 2 * blockIdx.x];
+        tok0 = prm.group_tiles[2 + 2 * blockIdx.x];
+        m_end = prm.group_offsets[group + 1];
+        w_shift = group * prm.group_w_rows;
+    }
+    const int feat0 = blockIdx.y * (WIDE ? 2 * BM : BM);
+    const int w_row0 = feat0 + w_shift;                                          // accumulator 0's rows of W
+    const int second_tile_row = (WIDE ? feat0 + BM : prm.up_row_offset + feat0) + w_shift;   // accumulator 1's
     const int splits = gridDim.z;
     const int total_kb = (prm.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * prm.k_blocks_per_split;
@@ -269,7 +287,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = tiles + (size_t)i * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[i], NORMED ? NACC * T::A_BYTES : T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
-                tma_load_2d(stage, &map_w, &full_bar[i], k, feat0);
+                tma_load_2d(stage, &map_w, &full_bar[i], k, w_row0);
                 if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[i], k, second_tile_row);
             }
             pdl_wait();
@@ -284,7 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = tiles + (size_t)s * T::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], NORMED ? NACC * T::A_BYTES : T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BK;
-                tma_load_2d(stage, &map_w, &full_bar[s], k, feat0);
+                tma_load_2d(stage, &map_w, &full_bar[s], k, w_row0);
                 if (NACC == 2) tma_load_2d(stage + T::A_BYTES, &map_w, &full_bar[s], k, second_tile_row);
                 if (!NORMED) tma_load_2d(stage + NACC * T::A_BYTES, &map_x, &full_bar[s], k, tok0);
             }
@@ -343,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // col: token inside the tile; g: accumulator 0; u: accumulator 1 (SwiGLU only);
         // r: the token's rsqrt(mean square + eps) (NORMED only)
         const int t = tok0 + col;
-        if (t >= prm.M || f >= prm.N) return;
+        if (t >= m_end || f >= prm.N) return;
         if (NORMED) {
             g *= r;
             u *= r;
@@ -421,7 +439,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const int col = col0 + b * col_step;
                     const bool live = col < BN;
                     add[b] = 0.0f;
-                    if (EPI == EPI_ADD_F32 && live && tok0 + col < prm.M && f < prm.N)
+                    if (EPI == EPI_ADD_F32 && live && tok0 + col < m_end && f < prm.N)
                         add[b] = prm.addend[(size_t)(tok0 + col) * prm.ldy + f];
 #pragma unroll
                     for (int r = 0; r < 8; ++r) {
@@ -578,6 +596,9 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.norm_w = nullptr;
     prm.norm_rows = nullptr;
     prm.norm_eps = 0.0f;
+    prm.group_tiles = nullptr;
+    prm.group_offsets = nullptr;
+    prm.group_w_rows = 0;
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
     if (!make_map(&map_x, X, M, K, bn_eff)) return FWB_UNSUPPORTED;
@@ -632,6 +653,9 @@ FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, con
     prm.norm_w = norm_w;
     prm.norm_rows = rows;
     prm.norm_eps = eps;
+    prm.group_tiles = nullptr;
+    prm.group_offsets = nullptr;
+    prm.group_w_rows = 0;
     CUtensorMap map_w;
     if (!make_map(&map_w, W, w_rows, K, BM)) return FWB_UNSUPPORTED;
     switch (bn) {
@@ -687,4 +711,55 @@ FWB_API int fwb_selftest_bounded_wait(int code, cudaStream_t stream) {
 FWB_API int fwb_set_pdl(int enabled) {
     fwb::pdl_enabled() = enabled != 0;
     return FWB_OK;
+}
+
+// The grouped form, for products whose rows belong to groups with a weight matrix each (experts):
+// X: [A][K] bf16, rows sorted by group; W: [n_groups * group_w_rows][K] bf16, the groups' matrices one
+// below the other; offsets: [n_groups + 1] first row of every group; tiles: the list a sorting kernel
+// made for token tiles of `tile_rows` rows (16, 32, 64 or 128): tiles[0] tiles, then (group, first row)
+// pairs; max_tiles: the most the list can hold (the grid).  Y: [A][ldy], fp32 (epilogue 0) or bf16 (1, 3).
+// epilogue 3: gate rows at 0 and up rows at up_row_offset inside a group's matrix, N = F; the gate's
+// activation rides in the bits above the code as in fwb_gemm_tcgen05.  One slice of K, no split.
+FWB_API int fwb_gemm_tcgen05_grouped(const void* X, const void* W, void* Y, const int* offsets, const int* tiles,
+                                     int max_tiles, int tile_rows, int A, int N, int K, int n_groups,
+                                     int group_w_rows, int ldy, int epilogue, int up_row_offset,
+                                     cudaStream_t stream) {
+    const int gate_act = epilogue >> 8;
+    epilogue &= 0xff;
+    if (A <= 0 || N <= 0 || max_tiles <= 0 || n_groups <= 0) return FWB_OK;
+    if (!X || !W || !Y || !offsets || !tiles || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
+    if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;
+    if (epilogue != EPI_F32 && epilogue != EPI_BF16 && epilogue != EPI_SWIGLU_BF16) return FWB_UNSUPPORTED;
+    if (epilogue == EPI_SWIGLU_BF16 && (up_row_offset < N || group_w_rows < up_row_offset + N)) return FWB_BAD_ARGUMENT;
+    if (epilogue != EPI_SWIGLU_BF16 && group_w_rows < N) return FWB_BAD_ARGUMENT;
+    if (tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128) return FWB_BAD_ARGUMENT;
+    if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
+    Params prm;
+    prm.y = Y;
+    prm.addend = nullptr;
+    prm.M = max_tiles * tile_rows;          // the grid's token tiles; a tile's own end comes from `offsets`
+    prm.N = N;
+    prm.K = K;
+    prm.ldy = ldy;
+    prm.up_row_offset = up_row_offset;
+    prm.gate_act = gate_act;
+    prm.k_blocks_per_split = (K + BK - 1) / BK;
+    prm.stages = 0;
+    prm.status = status_word();
+    prm.norm_x = nullptr;
+    prm.norm_w = nullptr;
+    prm.norm_rows = nullptr;
+    prm.norm_eps = 0.0f;
+    prm.group_tiles = tiles;
+    prm.group_offsets = offsets;
+    prm.group_w_rows = group_w_rows;
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, W, (long)n_groups * group_w_rows, K, BM)) return FWB_UNSUPPORTED;
+    if (!make_map(&map_x, X, A, K, tile_rows)) return FWB_UNSUPPORTED;
+    switch (tile_rows) {
+        case 16: return launch_epi<16>(epilogue, map_w, map_x, prm, 1, stream);
+        case 32: return launch_epi<32>(epilogue, map_w, map_x, prm, 1, stream);
+        case 64: return launch_epi<64>(epilogue, map_w, map_x, prm, 1, stream);
+        default: return launch_epi<128>(epilogue, map_w, map_x, prm, 1, stream);
+    }
 }

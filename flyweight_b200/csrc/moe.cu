@@ -123,9 +123,10 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
 //   offsets[E + 1]   first row of every expert among the sorted rows
 //   row_token[A]     token of every sorted row
 //   pair_row[A]      sorted row of every pair (-1: an identity expert)
-//   tiles[0]         number of row tiles; tiles[1 + 2 i], tiles[2 + 2 i]: expert and first row of tile i
+//   tiles[0]         number of row tiles (of tile_rows rows at most, none across two experts);
+//                    tiles[1 + 2 i], tiles[2 + 2 i]: expert and first row of tile i
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int A, int top, int E, int* __restrict__ offsets,
+moe_sort_kernel(const int* __restrict__ ids, int A, int top, int E, int tile_rows, int* __restrict__ offsets,
                 int* __restrict__ row_token, int* __restrict__ pair_row, int* __restrict__ tiles) {
     fwb::pdl_entry();
     extern __shared__ int counts[];               // [E] counts, then [E] cursors
@@ -143,7 +144,7 @@ moe_sort_kernel(const int* __restrict__ ids, int A, int top, int E, int* __restr
             const int n = counts[e];
             offsets[e] = at;
             cursor[e] = at;
-            for (int row = 0; row < n; row += TM) {
+            for (int row = 0; row < n; row += tile_rows) {
                 tiles[1 + 2 * n_tiles] = e;
                 tiles[2 + 2 * n_tiles] = at + row;
                 ++n_tiles;
@@ -163,6 +164,16 @@ moe_sort_kernel(const int* __restrict__ ids, int A, int top, int E, int* __restr
         }
         pair_row[a] = row;
     }
+}
+
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const uint4* __restrict__ h, const int* __restrict__ row_token, const int* __restrict__ offsets,
+                       int E, uint4* __restrict__ out, int pieces) {
+    fwb::pdl_entry();
+    const int row = blockIdx.x;
+    if (row >= offsets[E]) return;            // rows behind the last expert's belong to nobody
+    const uint4* src = h + (size_t)row_token[row] * pieces;
+    for (int i = threadIdx.x; i < pieces; i += blockDim.x) out[(size_t)row * pieces + i] = src[i];
 }
 
 // FORM 1: out[row][f] = act(x . gate_f) * (x . up_f), w: [E][2F][K] (gate rows, then up rows), N = F.
@@ -281,23 +292,32 @@ FWB_API int fwb_moe_route(const void* h, int h_bf16, const float* router, const 
     return fwb_launch_status();
 }
 
-// The number of row tiles the products' grids must allow for `pairs` (token, expert) pairs.
-FWB_API int fwb_moe_max_tiles(int pairs, int E) { return (pairs + TM - 1) / TM + E; }
-
-// ids: [A]; offsets: [E + 1]; row_token, pair_row: [A]; tiles: [1 + 2 fwb_moe_max_tiles(A, E)].
-FWB_API int fwb_moe_sort(const int* ids, int A, int top, int E, int* offsets, int* row_token, int* pair_row,
-                         int* tiles, cudaStream_t stream) {
+// ids: [A]; offsets: [E + 1]; row_token, pair_row: [A]; tiles: [1 + 2 (A / tile_rows + E + 1)].
+// tile_rows: rows of a tile of the products that follow (TM = 64 for fwb_moe_gemm).
+FWB_API int fwb_moe_sort(const int* ids, int A, int top, int E, int tile_rows, int* offsets, int* row_token,
+                         int* pair_row, int* tiles, cudaStream_t stream) {
     if (A <= 0) return FWB_OK;
-    if (!ids || !offsets || !row_token || !pair_row || !tiles || top <= 0 || E < 0) return FWB_BAD_ARGUMENT;
+    if (!ids || !offsets || !row_token || !pair_row || !tiles || top <= 0 || E < 0 || tile_rows <= 0)
+        return FWB_BAD_ARGUMENT;
     if (E > 4096) return FWB_TOO_LARGE;
-    fwb::pdl(moe_sort_kernel, 1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream)(ids, A, top, E, offsets,
+    fwb::pdl(moe_sort_kernel, 1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream)(ids, A, top, E, tile_rows, offsets,
                                                                                   row_token, pair_row, tiles);
+    return fwb_launch_status();
+}
+
+// out[row] = h[row_token[row]] for the sorted rows (16-byte pieces): the experts' first product then
+// reads its rows side by side.  h: [T][W] bf16, W a multiple of 8; out: [A][W].
+FWB_API int fwb_moe_gather_rows(const void* h, const int* row_token, const int* offsets, int E, void* out, int A,
+                                int W, cudaStream_t stream) {
+    if (A <= 0) return FWB_OK;
+    if (!h || !row_token || !offsets || !out || W <= 0 || (W & 7)) return FWB_BAD_ARGUMENT;
+    fwb::pdl(moe_gather_rows_kernel, A, 128, 0, stream)((const uint4*)h, row_token, offsets, E, (uint4*)out, W / 8);
     return fwb_launch_status();
 }
 
 // form 1: x [T][K] (rows gathered by row_token), w [E][2N][K], out [A][N] in the dtype of x.
 // form 0: x [A][K] sorted rows, w [E][N][K], out [A][N] fp32.
-// x and w are both fp32 or both bf16.  max_tiles: fwb_moe_max_tiles of the step.
+// x and w are both fp32 or both bf16.  max_tiles: the most tiles the sorted list can hold (the grid).
 FWB_API int fwb_moe_gemm(const void* x, const void* w, int bf16, void* out, const int* offsets,
                          const int* row_token, const int* tiles, int max_tiles, int N, int K, int form, int act,
                          cudaStream_t stream) {

@@ -9,6 +9,16 @@ from .lib import KernelError, c_float, check_tensor, is_bf16, ptr, stream
 from .ops import GATE_ACTIVATIONS
 
 
+SIMT_TILE_ROWS = 64          # rows of a tile of fwb_moe_gemm
+_use_tensor_cores = True
+
+
+def set_tensor_cores(flag: bool) -> None:
+    """Tests switch the grouped tcgen05 product off to compare it with the fp32-FMA kernel."""
+    global _use_tensor_cores
+    _use_tensor_cores = bool(flag)
+
+
 def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int):
     """ids int32 [T][top] and weights fp32 [T][top]: softmax scores over all router outputs; the choice
     on score + correction inside the ``keep`` best of ``n_groups`` runs of neighbours; the weights are
@@ -41,19 +51,37 @@ def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     check_tensor("expert weights", weights, torch.float32, (T, top))
     act = GATE_ACTIVATIONS[activation]
     A = T * top
-    max_tiles = lib.library().fwb_moe_max_tiles(A, E)
+    bf16 = is_bf16(h)
+    # bfloat16 rows whose lengths the tensor maps take run the grouped tcgen05 product, on token tiles
+    # as wide as an expert's share of the step's rows; everything else the fp32-FMA kernel (tiles of 64)
+    tensor_cores = bool(bf16 and _use_tensor_cores and E > 0 and W % 8 == 0 and F % 8 == 0)
+    tile_rows = SIMT_TILE_ROWS
+    if tensor_cores:
+        share = -(-A // E)
+        tile_rows = 16 if share <= 16 else (32 if share <= 32 else (64 if share <= 64 else 128))
+    max_tiles = A // tile_rows + E + 1
     dev = h.device
     meta = torch.empty(E + 1 + 2 * A + 1 + 2 * max_tiles, dtype=torch.int32, device=dev)
     offsets, row_token = meta[:E + 1], meta[E + 1:E + 1 + A]
     pair_row, tiles = meta[E + 1 + A:E + 1 + 2 * A], meta[E + 1 + 2 * A:]
-    lib.call("fwb_moe_sort", ptr(ids), A, top, E, ptr(offsets), ptr(row_token), ptr(pair_row), ptr(tiles), stream())
-    bf16 = is_bf16(h)
+    lib.call("fwb_moe_sort", ptr(ids), A, top, E, tile_rows, ptr(offsets), ptr(row_token), ptr(pair_row), ptr(tiles),
+             stream())
     a = torch.empty((A, F), dtype=h.dtype, device=dev)
-    lib.call("fwb_moe_gemm", ptr(h), ptr(w_gate_up), bf16, ptr(a), ptr(offsets), ptr(row_token), ptr(tiles),
-             max_tiles, F, W, 1, act, stream())
     y = torch.empty((A, W), dtype=torch.float32, device=dev)
-    lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
-             max_tiles, W, F, 0, 0, stream())
+    if tensor_cores:
+        from .tensorcore import EPI_F32, _gated_epilogue
+        rows = torch.empty((A, W), dtype=h.dtype, device=dev)
+        lib.call("fwb_moe_gather_rows", ptr(h), ptr(row_token), ptr(offsets), E, ptr(rows), A, W, stream())
+        lib.call("fwb_gemm_tcgen05_grouped", ptr(rows), ptr(w_gate_up), ptr(a), ptr(offsets), ptr(tiles), max_tiles,
+                 tile_rows, A, F, W, E, 2 * F, F, _gated_epilogue(activation), F, stream(),
+                 tag=f"experts gate|up {F}x{W}")
+        lib.call("fwb_gemm_tcgen05_grouped", ptr(a), ptr(w_down), ptr(y), ptr(offsets), ptr(tiles), max_tiles,
+                 tile_rows, A, W, F, E, W, W, EPI_F32, 0, stream(), tag=f"experts down {W}x{F}")
+    elif E > 0:                                 # (a router may have identity experts only)
+        lib.call("fwb_moe_gemm", ptr(h), ptr(w_gate_up), bf16, ptr(a), ptr(offsets), ptr(row_token), ptr(tiles),
+                 max_tiles, F, W, 1, act, stream())
+        lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
+                 max_tiles, W, F, 0, 0, stream())
     out = torch.empty((T, W), dtype=torch.float32, device=dev)
     lib.call("fwb_moe_combine", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(out), T, W, top,
              E, stream())

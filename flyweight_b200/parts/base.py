@@ -148,6 +148,11 @@ class Part:
         """Bytes of device weights a step reads (for roofline accounting)."""
         return 0
 
+    def active_weight_bytes(self, n_tokens: int) -> int:
+        """Bytes of weights a step of ``n_tokens`` tokens reads at most (less than ``weight_bytes()`` for a
+        part whose tokens choose among its weights)."""
+        return self.weight_bytes()
+
     def flops_per_token(self) -> float:
         """Floating-point operations of this part's matrix products for one token (2 per weight)."""
         return 0.0

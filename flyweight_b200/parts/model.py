@@ -93,14 +93,16 @@ class DecoderModel:
         """For each schedule position the earlier position whose pages it reads, or None."""
         return [entry.cache_of for entry in self.spec.schedule]
 
-    def weight_bytes(self, with_embedding_rows: int = 0) -> int:
+    def weight_bytes(self, with_embedding_rows: int = 0, tokens: Optional[int] = None) -> int:
         """Bytes of weights one step reads: every scheduled layer once, the final norm, the
-        head, and ``with_embedding_rows`` rows of the embedding table."""
+        head, and ``with_embedding_rows`` rows of the embedding table.  ``tokens``: the step's token
+        count, for parts that touch only the weights their tokens choose (routed experts)."""
         total = self.final_norm.weight_bytes()
         total += self.head.numel() * self.head.element_size()
         total += with_embedding_rows * self.spec.hidden_size * self.embedding.element_size()
         for entry in self.spec.schedule:
-            total += sum(part.weight_bytes() for part in self.layers[entry.layer].parts())
+            total += sum(part.weight_bytes() if tokens is None else part.active_weight_bytes(tokens)
+                         for part in self.layers[entry.layer].parts())
         return total
 
     def flops_per_token(self, with_head: bool = False) -> float:

@@ -85,6 +85,11 @@ class RoutedExperts(FeedForward):
         return (self.router.numel() * 4 + self.w_gate_up.numel() * self.w_gate_up.element_size()
                 + self.w_down.numel() * self.w_down.element_size())
 
+    def active_weight_bytes(self, n_tokens):
+        chosen = min(self.n_experts, n_tokens * self.top)
+        per_expert = 3 * self.ffn_dim * self.hidden * self.w_gate_up.element_size()
+        return self.router.numel() * 4 + chosen * per_expert
+
     def flops_per_token(self):
         return 2.0 * self.router.numel() + 2.0 * self.top * 3 * self.ffn_dim * self.hidden
 

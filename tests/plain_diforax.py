@@ -84,17 +84,17 @@ def chunk_visible(q_positions, k_positions, chunk):
     return (j <= i) & (torch.div(i, chunk, rounding_mode="floor") == torch.div(j, chunk, rounding_mode="floor"))
 
 
-def attention_keys(h, positions, w_k, w_v, G, d, e, base, dims, eps):
+def attention_keys(h, positions, w_k, w_v, G, d, e, base, dims, eps, rnd=same):
     """What an attention layer caches for the rows ``h``: keys (turned, then brought to unit root
-    mean square per head) [T][G][d] and values [T][G][e]."""
+    mean square per head) [T][G][d] and values [T][G][e].  ``rnd`` rounds the projections' results."""
     T = h.shape[0]
-    k = rms_unit(rotate((h @ w_k.T).view(T, G, d), positions, base, dims), eps)
-    return k, (h @ w_v.T).view(T, G, e)
+    k = rms_unit(rotate(rnd(h @ w_k.T).view(T, G, d), positions, base, dims), eps)
+    return k, rnd(h @ w_v.T).view(T, G, e)
 
 
-def attention_queries(h, positions, w_q, H, d, base, dims, eps):
+def attention_queries(h, positions, w_q, H, d, base, dims, eps, rnd=same):
     T = h.shape[0]
-    return rms_unit(rotate((h @ w_q.T).view(T, H, d), positions, base, dims), eps)
+    return rms_unit(rotate(rnd(h @ w_q.T).view(T, H, d), positions, base, dims), eps)
 
 
 def chunked_attention(q, q_positions, k, v, k_positions, scale, chunk):
@@ -231,10 +231,10 @@ def forward(config, weights, tokens, dtype=torch.float64, keep_layers=False, rnd
             if m.get("kv_from") is not None:
                 k, v = cached[int(m["kv_from"])]
             else:
-                k, v = attention_keys(h, positions, mix["k"], mix["v"], G, d, e, base, dims, eps)
+                k, v = attention_keys(h, positions, mix["k"], mix["v"], G, d, e, base, dims, eps, rnd)
                 k, v = rnd(k), rnd(v)
                 cached[index] = (k, v)
-            q = rnd(attention_queries(h, positions, mix["q"], H, d, base, dims, eps))
+            q = rnd(attention_queries(h, positions, mix["q"], H, d, base, dims, eps, rnd))
             chunk = int((m.get("mask") or {}).get("size") or T + 1)
             y = rnd(chunked_attention(q, positions, k, v, positions, float(m["scale"]), chunk)) @ mix["o"].T
         elif layer["type"] == "delta":
