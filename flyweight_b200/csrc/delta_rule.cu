@@ -9,15 +9,15 @@
 // itself) and silu; q and k are then made unit vectors per head (x / sqrt(sum x^2 + 1e-6)); query
 // head h uses q/k head h / (H / G).  beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
 //
-// Four kernels (everything fp32):
+// Three kernels (everything fp32):
 //   delta_prepare   one block per token: convolution + silu, unit vectors, beta and g
 //                   -> r[t] = [ q^: G d | k^: G d | v: H e | beta: H | g: H ]
-//   delta_conv_advance  one thread per (segment, channel): the request's last L-1 inputs, for the
-//                   next step (runs behind delta_prepare, which reads the old ones)
-//   delta_scan      one block per (32 columns of S, head, segment): the recurrence over the
+//   delta_scan      one block per (16 or 32 columns of S, head, segment): the recurrence over the
 //                   segment's tokens in order.  A column of S evolves independently of the others;
-//                   four adjacent lanes hold one column (d/4 entries each in registers), so a token
-//                   costs two 4-lane reductions.  State in and out of the request's slot.
+//                   four or eight adjacent lanes hold one column in registers, so a token costs two
+//                   reductions over those lanes.  State in and out of the request's slot.  The first
+//                   block of a segment also moves the convolution's last L-1 inputs on, for the next
+//                   step (behind delta_prepare, which reads the old ones).
 //   gated_head_norm out[t][h] = weight * o / sqrt(mean(o^2) + eps) * silu(gate)
 // A request's slot is [ S: H d e | conv inputs: C (L-1) ] fp32, zero when the request starts.  A
 // token's result depends on its request's earlier tokens only through that slot, and every sum runs
@@ -36,10 +36,11 @@ struct DeltaShape {
     __host__ __device__ int cv() const { return H * e; }
     __host__ __device__ int channels() const { return 2 * G * d + H * e; }      // through the convolution
     __host__ __device__ int p_width() const { return channels() + H * e + 2 * H; }
-    __host__ __device__ int r_width() const { return channels() + 2 * H; }
+    // (rows of r are padded to 16 bytes, so that 16-byte copies may start at a head's first channel)
+    __host__ __device__ int r_width() const { return (channels() + 2 * H + 3) & ~3; }
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 delta_prepare_kernel(const float* __restrict__ p, const float* __restrict__ taps, const float* __restrict__ a_log,
                      const float* __restrict__ dt_bias, const float* __restrict__ state, long long slot_stride,
                      const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
@@ -83,98 +84,164 @@ delta_prepare_kernel(const float* __restrict__ p, const float* __restrict__ taps
     }
 }
 
-__global__ void __launch_bounds__(128)
-delta_conv_advance_kernel(const float* __restrict__ p, float* __restrict__ state, long long slot_stride,
-                          const int* __restrict__ seg_start, const int* __restrict__ seg_slot, DeltaShape sh) {
-    fwb::pdl_entry();
-    const int seg = blockIdx.y;
-    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ch >= sh.channels()) return;
-    const int t0 = seg_start[seg], n = seg_start[seg + 1] - t0, keep = sh.L - 1, P = sh.p_width();
-    if (n <= 0) return;
-    float* hist = state + (size_t)seg_slot[seg] * slot_stride + (size_t)sh.H * sh.d * sh.e + (size_t)ch * keep;
-    float next[MAX_TAPS];
-    for (int j = 0; j < keep; ++j) {
-        const int local = n - keep + j;           // the input that becomes entry j (oldest first)
-        next[j] = local >= 0 ? p[(size_t)(t0 + local) * P + ch] : hist[j + n];
+// The request's last L-1 inputs of every channel, for the next step.  Runs in the kernel behind
+// delta_prepare (which reads the old ones): the first block of every segment's scan does it.
+__device__ __forceinline__ void delta_conv_advance(const float* __restrict__ p, float* __restrict__ slot, int t0,
+                                                   int n, const DeltaShape& sh) {
+    const int keep = sh.L - 1, P = sh.p_width();
+    for (int ch = threadIdx.x; ch < sh.channels(); ch += blockDim.x) {
+        float* hist = slot + (size_t)sh.H * sh.d * sh.e + (size_t)ch * keep;
+        float next[MAX_TAPS];
+        for (int j = 0; j < keep; ++j) {
+            const int local = n - keep + j;       // the input that becomes entry j (oldest first)
+            next[j] = local >= 0 ? p[(size_t)(t0 + local) * P + ch] : hist[j + n];
+        }
+        for (int j = 0; j < keep; ++j) hist[j] = next[j];
     }
-    for (int j = 0; j < keep; ++j) hist[j] = next[j];
 }
 
-template <int DPL>
+__device__ __forceinline__ void copy_async_f32(float* dst_shared, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_async_16(float* dst_shared, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// LPC adjacent lanes hold one column of S, DPL consecutive entries each (LPC * DPL >= d).  The tokens'
+// q, k, v, beta and g arrive through a ring of asynchronous copies that runs three tokens ahead of the
+// arithmetic, so a token costs its FMAs, log2(LPC) shuffles per reduction and one block barrier.
+// In a slot, S lies column by column: S[h][column][d].
+// VEC: d and e are multiples of 4 and slots start on 16-byte borders: copies and state accesses of 16 bytes.
+template <int DPL, int LPC, bool VEC>
 __global__ void __launch_bounds__(128)
-delta_scan_kernel(const float* __restrict__ r, float* __restrict__ state, long long slot_stride,
-                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ o,
-                  DeltaShape sh) {
+delta_scan_kernel(const float* __restrict__ r, const float* __restrict__ p, float* __restrict__ state,
+                  long long slot_stride, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                  float* __restrict__ o, DeltaShape sh) {
     fwb::pdl_entry();
-    constexpr int DP = 4 * DPL;
-    __shared__ float kq[2][2][DP];
-    __shared__ float vs[2][32];
-    __shared__ float bg[2][2];
+    constexpr int COLS = 128 / LPC, STRIDE = DPL + 4, STAGES = 4;     // (+4: lanes' float4 reads hit apart banks)
+    __shared__ __align__(16) float kq[STAGES][2][LPC * STRIDE];
+    __shared__ __align__(16) float vs[STAGES][COLS];
+    __shared__ float bg[STAGES][2];
     const int seg = blockIdx.z, h = blockIdx.y;
     const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
     if (t1 <= t0) return;
     const int d = sh.d, e = sh.e, R = sh.r_width();
     const int kv_head = h / (sh.H / sh.G);
-    const int col_local = threadIdx.x >> 2, sub = threadIdx.x & 3;
-    const int col = blockIdx.x * 32 + col_local;
+    const int col_local = threadIdx.x / LPC, sub = threadIdx.x % LPC;
+    const int col = blockIdx.x * COLS + col_local;
     const bool valid = col < e;
-    float* S_slot = state + (size_t)seg_slot[seg] * slot_stride + (size_t)h * d * e;
+    float* slot = state + (size_t)seg_slot[seg] * slot_stride;
+    if (blockIdx.x == 0 && h == 0 && sh.L > 1) delta_conv_advance(p, slot, t0, t1 - t0, sh);
+    float* S_col = slot + ((size_t)h * e + (valid ? col : 0)) * d;
     float S[DPL];
+    if (VEC) {
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int dd = sub + 4 * i;
-        S[i] = (valid && dd < d) ? S_slot[(size_t)dd * e + col] : 0.0f;
+        for (int i = 0; i < DPL; i += 4) {
+            const int dd = sub * DPL + i;
+            const float4 v = (valid && dd < d) ? *reinterpret_cast<const float4*>(S_col + dd) : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[i] = v.x, S[i + 1] = v.y, S[i + 2] = v.z, S[i + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int dd = sub * DPL + i;
+            S[i] = (valid && dd < d) ? S_col[dd] : 0.0f;
+        }
+    }
+    if (d < DPL * LPC || (int)(blockIdx.x + 1) * COLS > e) {
+        // entries behind the head's last channel and columns behind the last are never copied: zeros
+        for (int i = threadIdx.x; i < STAGES * 2 * LPC * STRIDE; i += blockDim.x) (&kq[0][0][0])[i] = 0.0f;
+        for (int i = threadIdx.x; i < STAGES * COLS; i += blockDim.x) (&vs[0][0])[i] = 0.0f;
+        __syncthreads();
     }
     const int q_at = kv_head * d, k_at = sh.cq() + kv_head * d, v_at = 2 * sh.cq() + h * e;
     const int beta_at = sh.channels() + h, g_at = sh.channels() + sh.H + h;
-    auto fetch = [&](int t, int buf) {
-        const float* row = r + (size_t)t * R;
-        for (int i = threadIdx.x; i < 2 * DP; i += blockDim.x) {
-            const int which = i / DP, dd = i - which * DP;
-            kq[buf][which][dd] = dd < d ? row[(which ? q_at : k_at) + dd] : 0.0f;
+    auto fetch = [&](int t, int stage) {
+        if (t < t1) {
+            const float* row = r + (size_t)t * R;
+            if (VEC) {
+                for (int i = threadIdx.x * 4; i < 2 * d; i += blockDim.x * 4) {
+                    const int which = i >= d ? 1 : 0, dd = i - which * d;
+                    copy_async_16(&kq[stage][which][(dd / DPL) * STRIDE + dd % DPL], row + (which ? q_at : k_at) + dd);
+                }
+                const int c4 = (threadIdx.x - 96) * 4;        // the fourth warp brings the values
+                if (threadIdx.x >= 96 && c4 < COLS && (int)blockIdx.x * COLS + c4 < e)
+                    copy_async_16(&vs[stage][c4], row + v_at + blockIdx.x * COLS + c4);
+            } else {
+                for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) {
+                    const int which = i >= d ? 1 : 0, dd = i - which * d;
+                    copy_async_f32(&kq[stage][which][(dd / DPL) * STRIDE + dd % DPL], row + (which ? q_at : k_at) + dd);
+                }
+                if (threadIdx.x < COLS && blockIdx.x * COLS + threadIdx.x < e)
+                    copy_async_f32(&vs[stage][threadIdx.x], row + v_at + blockIdx.x * COLS + threadIdx.x);
+            }
+            if (threadIdx.x == 64) copy_async_f32(&bg[stage][0], row + beta_at);
+            if (threadIdx.x == 65) copy_async_f32(&bg[stage][1], row + g_at);
         }
-        if (threadIdx.x < 32) {
-            const int cc = blockIdx.x * 32 + threadIdx.x;
-            vs[buf][threadIdx.x] = cc < e ? row[v_at + cc] : 0.0f;
-        }
-        if (threadIdx.x == 32) bg[buf][0] = row[beta_at];
-        if (threadIdx.x == 33) bg[buf][1] = row[g_at];
+        copy_async_commit();
     };
-    fetch(t0, 0);
-    __syncthreads();
+    for (int j = 0; j < STAGES - 1; ++j) fetch(t0 + j, j);
     for (int t = t0; t < t1; ++t) {
-        const int buf = (t - t0) & 1;
-        if (t + 1 < t1) fetch(t + 1, buf ^ 1);
-        const float beta = bg[buf][0], g = bg[buf][1];
-        const float* k = kq[buf][0];
-        const float* q = kq[buf][1];
+        const int stage = (t - t0) % STAGES;
+        copy_async_wait<STAGES - 2>();          // this token's copies have landed (mine; the barrier: everybody's)
+        __syncthreads();                        // ... and everybody is done with the token before
+        fetch(t + STAGES - 1, (t - t0 + STAGES - 1) % STAGES);
+        const float beta = bg[stage][0], g = bg[stage][1];
+        const float4* k4 = reinterpret_cast<const float4*>(&kq[stage][0][sub * STRIDE]);
+        const float4* q4 = reinterpret_cast<const float4*>(&kq[stage][1][sub * STRIDE]);
         float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            S[i] *= g;
-            part[i & 3] = fmaf(S[i], k[sub + 4 * i], part[i & 3]);
+        for (int i = 0; i < DPL / 4; ++i) {
+            const float4 k = k4[i];
+            S[4 * i] *= g;
+            S[4 * i + 1] *= g;
+            S[4 * i + 2] *= g;
+            S[4 * i + 3] *= g;
+            part[0] = fmaf(S[4 * i], k.x, part[0]);
+            part[1] = fmaf(S[4 * i + 1], k.y, part[1]);
+            part[2] = fmaf(S[4 * i + 2], k.z, part[2]);
+            part[3] = fmaf(S[4 * i + 3], k.w, part[3]);
         }
         float dot = (part[0] + part[1]) + (part[2] + part[3]);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        const float u = beta * (vs[buf][col_local] - dot);
+#pragma unroll
+        for (int offset = 1; offset < LPC; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+        const float u = beta * (vs[stage][col_local] - dot);
         part[0] = part[1] = part[2] = part[3] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            S[i] = fmaf(k[sub + 4 * i], u, S[i]);
-            part[i & 3] = fmaf(S[i], q[sub + 4 * i], part[i & 3]);
+        for (int i = 0; i < DPL / 4; ++i) {
+            const float4 k = k4[i], q = q4[i];
+            S[4 * i] = fmaf(k.x, u, S[4 * i]);
+            S[4 * i + 1] = fmaf(k.y, u, S[4 * i + 1]);
+            S[4 * i + 2] = fmaf(k.z, u, S[4 * i + 2]);
+            S[4 * i + 3] = fmaf(k.w, u, S[4 * i + 3]);
+            part[0] = fmaf(S[4 * i], q.x, part[0]);
+            part[1] = fmaf(S[4 * i + 1], q.y, part[1]);
+            part[2] = fmaf(S[4 * i + 2], q.z, part[2]);
+            part[3] = fmaf(S[4 * i + 3], q.w, part[3]);
         }
         float out = (part[0] + part[1]) + (part[2] + part[3]);
-        out += __shfl_xor_sync(0xffffffffu, out, 1);
-        out += __shfl_xor_sync(0xffffffffu, out, 2);
-        if (sub == 0 && valid) o[((size_t)t * sh.H + h) * e + col] = out;
-        __syncthreads();
-    }
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int dd = sub + 4 * i;
-        if (valid && dd < d) S_slot[(size_t)dd * e + col] = S[i];
+        for (int offset = 1; offset < LPC; offset <<= 1) out += __shfl_xor_sync(0xffffffffu, out, offset);
+        if (sub == 0 && valid) o[((size_t)t * sh.H + h) * e + col] = out;
+    }
+    copy_async_wait<0>();
+    if (VEC) {
+#pragma unroll
+        for (int i = 0; i < DPL; i += 4) {
+            const int dd = sub * DPL + i;
+            if (valid && dd < d) *reinterpret_cast<float4*>(S_col + dd) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int dd = sub * DPL + i;
+            if (valid && dd < d) S_col[dd] = S[i];
+        }
     }
 }
 
@@ -199,7 +266,7 @@ gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ ga
 
 // p: [T][2Gd + 2He + 2H] fp32 (q | k | v | gate | b | a).  taps: [2Gd + He][L] fp32.  a_log, dt_bias: [H].
 // state: [slots][slot_stride] fp32 with S at 0 and the convolution's inputs behind it.
-// r: [T][2Gd + He + 2H] fp32 scratch.  o: [T][H][e] fp32.
+// r: [T][2Gd + He + 2H rounded up to a multiple of 4] fp32 scratch.  o: [T][H][e] fp32.
 FWB_API int fwb_delta_rule(const float* p, const float* taps, const float* a_log, const float* dt_bias,
                            float* state, long long slot_stride, const int* seg_start, const int* seg_slot,
                            const int* tok_seg, float* r, float* o, int T, int n_segments, int H, int G, int d,
@@ -215,18 +282,26 @@ FWB_API int fwb_delta_rule(const float* p, const float* taps, const float* a_log
     if (smem > 160 * 1024 || n_segments > 65535 || H > 65535) return FWB_TOO_LARGE;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    fwb::pdl(delta_prepare_kernel, T, 128, smem, stream)(p, taps, a_log, dt_bias, state, slot_stride, seg_start,
-                                                         seg_slot, tok_seg, r, sh);
-    if (L > 1)
-        fwb::pdl(delta_conv_advance_kernel, dim3((sh.channels() + 127) / 128, n_segments), 128, 0, stream)(
-            p, state, slot_stride, seg_start, seg_slot, sh);
-    const dim3 grid((e + 31) / 32, H, n_segments);
-#define FWB_SCAN(DPL) \
-    fwb::pdl(delta_scan_kernel<DPL>, grid, 128, 0, stream)(r, state, slot_stride, seg_start, seg_slot, o, sh)
-    if (d <= 32) FWB_SCAN(8);
-    else if (d <= 64) FWB_SCAN(16);
-    else if (d <= 128) FWB_SCAN(32);
-    else FWB_SCAN(64);
+    const int prepare_threads = sh.channels() >= 2048 ? 512 : (sh.channels() >= 512 ? 256 : 128);
+    fwb::pdl(delta_prepare_kernel, T, prepare_threads, smem, stream)(p, taps, a_log, dt_bias, state, slot_stride,
+                                                                     seg_start, seg_slot, tok_seg, r, sh);
+    const bool vec = d % 4 == 0 && e % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state & 15) == 0 &&
+                     ((uintptr_t)r & 15) == 0;
+#define FWB_SCAN(DPL, LPC)                                                                                 \
+    do {                                                                                                   \
+        const dim3 grid((e + 128 / LPC - 1) / (128 / LPC), H, n_segments);                                 \
+        if (vec)                                                                                           \
+            fwb::pdl(delta_scan_kernel<DPL, LPC, true>, grid, 128, 0, stream)(r, p, state, slot_stride,    \
+                                                                              seg_start, seg_slot, o, sh); \
+        else                                                                                               \
+            fwb::pdl(delta_scan_kernel<DPL, LPC, false>, grid, 128, 0, stream)(r, p, state, slot_stride,   \
+                                                                               seg_start, seg_slot, o, sh); \
+    } while (0)
+    if (d <= 16) FWB_SCAN(4, 4);
+    else if (d <= 32) FWB_SCAN(8, 4);
+    else if (d <= 64) FWB_SCAN(16, 4);
+    else if (d <= 128) FWB_SCAN(16, 8);
+    else FWB_SCAN(32, 8);
 #undef FWB_SCAN
     return fwb_launch_status();
 }

@@ -27,27 +27,60 @@ namespace {
 constexpr int TM = 64, TN = 64, TK = 16;       // tile of the experts' products
 
 template <typename TH>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int T, int W, int N, int n_groups, int keep,
                  int top) {
     fwb::pdl_entry();
-    extern __shared__ float shared[];             // per warp: s[N], choice[N], group value[n_groups]
+    // One block per token.  Its warps share the router's outputs between them (output n: lanes stride
+    // over k with sixteen sums in flight, added in one fixed order); warp 0 then chooses.
+    extern __shared__ float shared[];             // s[N], choice[N], group value[n_groups]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
-    float* s = shared + (size_t)warp * (2 * N + n_groups);
+    const int t = blockIdx.x;
+    float* s = shared;
     float* choice = s + N;
     float* best = choice + N;
     const TH* row = h + (size_t)t * W;
-    for (int n = 0; n < N; ++n) {
-        const float* w = router + (size_t)n * W;
-        float acc = 0.0f;
-        for (int k = lane; k < W; k += 32) acc = fmaf(to_f32<TH>(row[k]), w[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[n] = acc;
+    const int warps = blockDim.x >> 5;
+    for (int n = 2 * warp; n < N; n += 2 * warps) {
+        // two outputs at a time: their weights and the token's row, sixteen strides of 32 each, in flight together
+        const bool two = n + 1 < N;
+        const float* w0 = router + (size_t)n * W;
+        const float* w1 = router + (size_t)(two ? n + 1 : n) * W;
+        float p0[16], p1[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) p0[j] = p1[j] = 0.0f;
+        int k = lane;
+        for (; k + 15 * 32 < W; k += 16 * 32) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float x = to_f32<TH>(row[k + 32 * j]);
+                p0[j] = fmaf(x, w0[k + 32 * j], p0[j]);
+                p1[j] = fmaf(x, w1[k + 32 * j], p1[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (k + 32 * j < W) {
+                const float x = to_f32<TH>(row[k + 32 * j]);
+                p0[j] = fmaf(x, w0[k + 32 * j], p0[j]);
+                p1[j] = fmaf(x, w1[k + 32 * j], p1[j]);
+            }
+#pragma unroll
+        for (int step = 8; step > 0; step >>= 1)
+#pragma unroll
+            for (int j = 0; j < step; ++j) {
+                p0[j] += p0[j + step];
+                p1[j] += p1[j + step];
+            }
+        const float a0 = warp_sum(p0[0]), a1 = warp_sum(p1[0]);
+        if (lane == 0) {
+            s[n] = a0;
+            if (two) s[n + 1] = a1;
+        }
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float m = -INFINITY;
     for (int n = lane; n < N; n += 32) m = fmaxf(m, s[n]);
     m = warp_max(m);
@@ -256,14 +289,74 @@ moe_combine_kernel(const float* __restrict__ y, const TH* __restrict__ h, const 
                    const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ out, int W,
                    int top, int E) {
     fwb::pdl_entry();
+    constexpr int MAX_TOP = 64;
+    __shared__ int rows[MAX_TOP];                 // the sorted row of every slot; -1: identity; -2: nothing
+    __shared__ float wts[MAX_TOP];
     const int t = blockIdx.x;
+    if (threadIdx.x < top) {
+        const int a = t * top + threadIdx.x;
+        const int row = pair_row[a];
+        rows[threadIdx.x] = row >= 0 ? row : (ids[a] >= E ? -1 : -2);
+        wts[threadIdx.x] = weights[a];
+    }
+    __syncthreads();
+    if ((W & 3) == 0 && sizeof(TH) == 4) {
+        // rows of 16-byte pieces (the fp32 path's h as well as y)
+        const float4* y4 = reinterpret_cast<const float4*>(y);
+        const float4* h4 = reinterpret_cast<const float4*>(h);
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int slot = 0; slot < top; ++slot) {
+                const int row = rows[slot];
+                if (row == -2) continue;
+                const float4 v = row >= 0 ? y4[(size_t)row * (W / 4) + i] : h4[(size_t)t * (W / 4) + i];
+                const float wt = wts[slot];
+                acc.x = fmaf(wt, v.x, acc.x), acc.y = fmaf(wt, v.y, acc.y);
+                acc.z = fmaf(wt, v.z, acc.z), acc.w = fmaf(wt, v.w, acc.w);
+            }
+            reinterpret_cast<float4*>(out)[(size_t)t * (W / 4) + i] = acc;
+        }
+        return;
+    }
+    if ((W & 3) == 0) {
+        const float4* y4 = reinterpret_cast<const float4*>(y);
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int slot = 0; slot < top; ++slot) {
+                const int row = rows[slot];
+                if (row == -2) continue;
+                float4 v;
+                if (row >= 0) {
+                    v = y4[(size_t)row * (W / 4) + i];
+                } else {
+                    const TH* own = h + (size_t)t * W + 4 * i;
+                    v = make_float4(to_f32<TH>(own[0]), to_f32<TH>(own[1]), to_f32<TH>(own[2]), to_f32<TH>(own[3]));
+                }
+                const float wt = wts[slot];
+                acc.x = fmaf(wt, v.x, acc.x), acc.y = fmaf(wt, v.y, acc.y);
+                acc.z = fmaf(wt, v.z, acc.z), acc.w = fmaf(wt, v.w, acc.w);
+            }
+            reinterpret_cast<float4*>(out)[(size_t)t * (W / 4) + i] = acc;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float acc = 0.0f;
+        float own = 0.0f;
+        bool have = false;
         for (int slot = 0; slot < top; ++slot) {
-            const int a = t * top + slot;
-            const int row = pair_row[a];
-            const float v = row >= 0 ? y[(size_t)row * W + i] : (ids[a] >= E ? to_f32<TH>(h[(size_t)t * W + i]) : 0.0f);
-            acc = fmaf(weights[a], v, acc);
+            const int row = rows[slot];
+            float v = 0.0f;
+            if (row >= 0) {
+                v = y[(size_t)row * W + i];
+            } else if (row == -1) {
+                if (!have) {
+                    own = to_f32<TH>(h[(size_t)t * W + i]);
+                    have = true;
+                }
+                v = own;
+            }
+            acc = fmaf(wts[slot], v, acc);
         }
         out[(size_t)t * W + i] = acc;
     }
@@ -280,14 +373,15 @@ FWB_API int fwb_moe_route(const void* h, int h_bf16, const float* router, const 
     if (W <= 0 || N <= 0 || n_groups <= 0 || N % n_groups || keep <= 0 || keep > n_groups || top <= 0 ||
         top > keep * (N / n_groups))
         return FWB_BAD_ARGUMENT;
-    const size_t smem = 4 * (size_t)(2 * N + n_groups) * sizeof(float);
+    const size_t smem = (size_t)(2 * N + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return FWB_TOO_LARGE;
-    const int blocks = (T + 3) / 4;
+    const int blocks = T;
+    const int threads = N >= 32 ? 512 : (N >= 16 ? 256 : 128);      // two outputs a warp at a time
     if (h_bf16)
-        fwb::pdl(moe_route_kernel<__nv_bfloat16>, blocks, 128, smem, stream)(
+        fwb::pdl(moe_route_kernel<__nv_bfloat16>, blocks, threads, smem, stream)(
             (const __nv_bfloat16*)h, router, correction, ids, weights, T, W, N, n_groups, keep, top);
     else
-        fwb::pdl(moe_route_kernel<float>, blocks, 128, smem, stream)((const float*)h, router, correction, ids,
+        fwb::pdl(moe_route_kernel<float>, blocks, threads, smem, stream)((const float*)h, router, correction, ids,
                                                                       weights, T, W, N, n_groups, keep, top);
     return fwb_launch_status();
 }
@@ -348,6 +442,7 @@ FWB_API int fwb_moe_combine(const float* y, const void* h, int h_bf16, const int
                             const float* weights, float* out, int T, int W, int top, int E, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!y || !h || !pair_row || !ids || !weights || !out || W <= 0 || top <= 0) return FWB_BAD_ARGUMENT;
+    if (top > 64) return FWB_TOO_LARGE;
     if (h_bf16)
         fwb::pdl(moe_combine_kernel<__nv_bfloat16>, T, 256, 0, stream)(y, (const __nv_bfloat16*)h, pair_row, ids,
                                                                        weights, out, W, top, E);

@@ -167,6 +167,34 @@ def run_shortconv(args) -> dict:
             "gb_s": T * H * 2 * 4 / us / 1e3}
 
 
+def run_delta_rule(args) -> dict:
+    """The gated delta rule's two kernels (prepare; scan) over ``batch`` segments of ``tokens`` tokens."""
+    from ..engine.batch import Segment, StepBatch
+    from . import recurrent
+    H, G, d, e, L = args.heads, args.kv_heads, args.dim, args.vdim, args.taps
+    dev = torch.device("cuda", 0)
+    T = args.batch * args.tokens
+    channels = 2 * G * d + H * e
+    g = torch.Generator(device=dev).manual_seed(0)
+    p = torch.randn((T, channels + H * e + 2 * H), generator=g, device=dev, dtype=torch.float32)
+    taps = torch.randn((channels, L), generator=g, device=dev, dtype=torch.float32) * 0.5
+    a_log = torch.zeros(H, device=dev, dtype=torch.float32)
+    dt_bias = torch.zeros(H, device=dev, dtype=torch.float32)
+    state = torch.zeros((args.batch, recurrent.delta_state_size(H, G, d, e, L)), device=dev, dtype=torch.float32)
+    batch = StepBatch([Segment(f"r{i}", i, 0, [0] * args.tokens, []) for i in range(args.batch)],
+                      [[[0]] * args.batch], dev)
+
+    def step():
+        recurrent.delta_rule(p, taps, a_log, dt_bias, state, batch, H, G, d, e)
+
+    us = _time_graph(step, args.repeat) if args.graph else _time(step, args.repeat)
+    state_bytes = 2 * args.batch * H * d * e * 4
+    stream_bytes = T * (p.shape[1] + 2 * (channels + 2 * H) + H * e) * 4
+    return {"kernel": "delta_rule", "batch": args.batch, "tokens": args.tokens, "heads": H, "kv_heads": G, "dim": d,
+            "vdim": e, "taps": L, "us": us, "us_per_token": us / args.tokens,
+            "gb_s": (state_bytes + stream_bytes) / us / 1e3, "gflops": 6.0 * T * H * d * e / us / 1e3}
+
+
 def run_qk_norm_rope(args) -> dict:
     from . import ops
     T, nh, nkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
@@ -274,6 +302,15 @@ def main(argv=None) -> int:
     rope.add_argument("--heads", type=int, default=32)
     rope.add_argument("--kv-heads", type=int, default=8)
     rope.add_argument("--head-dim", type=int, default=64)
+    delta = sub.add_parser("delta-rule")
+    delta.add_argument("--batch", type=int, default=1)
+    delta.add_argument("--tokens", type=int, default=2048)
+    delta.add_argument("--heads", type=int, default=16)
+    delta.add_argument("--kv-heads", type=int, default=8)
+    delta.add_argument("--dim", type=int, default=128)
+    delta.add_argument("--vdim", type=int, default=128)
+    delta.add_argument("--taps", type=int, default=4)
+    delta.add_argument("--graph", action="store_true")
     smp = sub.add_parser("sample")
     smp.add_argument("--rows", type=int, default=8)
     smp.add_argument("--vocab", type=int, default=65536)
@@ -287,7 +324,7 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
               "attention-prefill": run_attention_prefill, "shortconv": run_shortconv,
-              "qk-norm-rope": run_qk_norm_rope, "sample": run_sample}[args.kernel]
+              "qk-norm-rope": run_qk_norm_rope, "sample": run_sample, "delta-rule": run_delta_rule}[args.kernel]
     print(json.dumps(runner(args)))
     return 0
 

@@ -10,9 +10,10 @@ from .ops import _i32
 
 
 def delta_state_size(heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> int:
-    """fp32 entries of one request's slot: the [heads][dim][vdim] state, then the convolution's last
-    ``taps - 1`` inputs of every channel of q, k and v."""
-    return heads * dim * vdim + (2 * kv_heads * dim + heads * vdim) * (taps - 1)
+    """fp32 entries of one request's slot: the [heads][vdim][dim] state, then the convolution's last
+    ``taps - 1`` inputs of every channel of q, k and v (rounded up to a multiple of 4)."""
+    size = heads * dim * vdim + (2 * kv_heads * dim + heads * vdim) * (taps - 1)
+    return -(-size // 4) * 4            # slots start on 16-byte borders
 
 
 def delta_rule(p: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
@@ -41,11 +42,11 @@ def delta_rule(p: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias
     _i32("seg_start", batch.seg_start, S + 1)
     _i32("seg_slot", batch.seg_slot, S)
     _i32("tok_seg", batch.tok_seg, T)
-    r = torch.empty((T, channels + 2 * heads), dtype=torch.float32, device=p.device)
+    r = torch.empty((T, -(-(channels + 2 * heads) // 4) * 4), dtype=torch.float32, device=p.device)
     o = torch.empty((T, heads, vdim), dtype=torch.float32, device=p.device)
     lib.call("fwb_delta_rule", ptr(p), ptr(taps), ptr(a_log), ptr(dt_bias), ptr(state), c_longlong(stride),
              ptr(batch.seg_start), ptr(batch.seg_slot), ptr(batch.tok_seg), ptr(r), ptr(o), T, S, heads, kv_heads,
-             dim, vdim, L, stream(), launches=3 if L > 1 else 2)
+             dim, vdim, L, stream(), launches=2)
     return o
 
 

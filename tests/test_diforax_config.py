@@ -93,8 +93,8 @@ def test_declared_tensors_and_their_shapes():
     assert declared["l1.mlp.gate"] == (raw["layers"][1]["mlp"]["ff"], W)
     # the state one request keeps in a delta layer: the matrices and the convolution's last inputs
     state = model.layers[0].state_spec()
-    assert state.shape == (d["heads"] * d["dim"] * d["vdim"]
-                           + (2 * d["kv_heads"] * d["dim"] + d["heads"] * d["vdim"]) * (d["conv"] - 1),)
+    entries = d["heads"] * d["dim"] * d["vdim"] + (2 * d["kv_heads"] * d["dim"] + d["heads"] * d["vdim"]) * (d["conv"] - 1)
+    assert state.shape == (-(-entries // 4) * 4,)                     # slots start on 16-byte borders
     pages = model.layers[1].state_spec()
     assert (pages.n_kv_heads, pages.head_dim, pages.window) == (a["kv_heads"], max(a["dim"], a["vdim"]), 0)
     assert model.layers[2].state_spec() is None
