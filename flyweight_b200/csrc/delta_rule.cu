@@ -11,7 +11,7 @@
 //
 // Three kernels (everything fp32):
 //   delta_prepare   one block per token: convolution + silu, unit vectors, beta and g
-//                   -> r[t] = [ q^: G d | k^: G d | v: H e | beta: H | g: H ]
+//                   -> r[t] = [ q^: G d | k^: G d | v: H e | beta: H | g: H | q^.k^: G ]
 //   delta_scan      one block per (16 or 32 columns of S, head, segment): the recurrence over the
 //                   segment's tokens in order.  A column of S evolves independently of the others;
 //                   four or eight adjacent lanes hold one column in registers, so a token costs two
@@ -37,7 +37,7 @@ struct DeltaShape {
     __host__ __device__ int channels() const { return 2 * G * d + H * e; }      // through the convolution
     __host__ __device__ int p_width() const { return channels() + H * e + 2 * H; }
     // (rows of r are padded to 16 bytes, so that 16-byte copies may start at a head's first channel)
-    __host__ __device__ int r_width() const { return (channels() + 2 * H + 3) & ~3; }
+    __host__ __device__ int r_width() const { return (channels() + 2 * H + G + 3) & ~3; }
 };
 
 __global__ void __launch_bounds__(512)
@@ -66,13 +66,22 @@ delta_prepare_kernel(const float* __restrict__ p, const float* __restrict__ taps
     float* out = r + (size_t)t * R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const float q_scale = rsqrtf((float)sh.d);
-    for (int unit = warp; unit < 2 * sh.G; unit += warps) {       // G query heads, then G key heads
-        const float* src = c + (size_t)unit * sh.d;
-        float ss = 0.0f;
-        for (int i = lane; i < sh.d; i += 32) ss = fmaf(src[i], src[i], ss);
-        ss = warp_sum(ss);
-        const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (unit < sh.G ? q_scale : 1.0f);
-        for (int i = lane; i < sh.d; i += 32) out[(size_t)unit * sh.d + i] = src[i] * inv;
+    for (int head = warp; head < sh.G; head += warps) {            // query head and key head `head` together
+        const float* q = c + (size_t)head * sh.d;
+        const float* k = c + (size_t)(sh.G + head) * sh.d;
+        float qq = 0.0f, kk = 0.0f, qk = 0.0f;
+        for (int i = lane; i < sh.d; i += 32) {
+            qq = fmaf(q[i], q[i], qq);
+            kk = fmaf(k[i], k[i], kk);
+            qk = fmaf(q[i], k[i], qk);
+        }
+        qq = warp_sum(qq), kk = warp_sum(kk), qk = warp_sum(qk);
+        const float inv_q = (1.0f / sqrtf(qq + 1e-6f)) * q_scale, inv_k = 1.0f / sqrtf(kk + 1e-6f);
+        for (int i = lane; i < sh.d; i += 32) {
+            out[(size_t)head * sh.d + i] = q[i] * inv_q;
+            out[(size_t)(sh.G + head) * sh.d + i] = k[i] * inv_k;
+        }
+        if (lane == 0) out[C + 2 * sh.H + head] = (qk * inv_q) * inv_k;      // q^ . k^, for the read-out
     }
     for (int i = threadIdx.x; i < sh.cv(); i += blockDim.x) out[2 * sh.cq() + i] = c[2 * sh.cq() + i];
     for (int h = threadIdx.x; h < sh.H; h += blockDim.x) {
@@ -113,20 +122,27 @@ template <int N>
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // LPC adjacent lanes hold one column of S, DPL consecutive entries each (LPC * DPL >= d).  The tokens'
-// q, k, v, beta and g arrive through a ring of asynchronous copies that runs three tokens ahead of the
-// arithmetic, so a token costs its FMAs, log2(LPC) shuffles per reduction and one block barrier.
-// In a slot, S lies column by column: S[h][column][d].
-// VEC: d and e are multiples of 4 and slots start on 16-byte borders: copies and state accesses of 16 bytes.
+// q, k, v, beta, g and q.k arrive through a ring of asynchronous copies that runs three tokens ahead of the
+// arithmetic.  Per token both sums over the *old* column, a = S.k and b = S.q, are taken in one pass and
+// reduced over the LPC lanes together; then
+//     u = beta (v - g a),   o = g b + u (q.k),   S <- g S + k u
+// which is the recurrence in the order the header states (the read-out sees the token's write), with
+// one reduction on the way to the next token instead of two.  In a slot, S lies column by column:
+// S[h][column][d].  VEC: d and e are multiples of 4 and slots start on 16-byte borders: copies and
+// state accesses of 16 bytes.
 template <int DPL, int LPC, bool VEC>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ r, const float* __restrict__ p, float* __restrict__ state,
                   long long slot_stride, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                   float* __restrict__ o, DeltaShape sh) {
-    fwb::pdl_entry();
+    // The next kernel is released only behind the token loop: its blocks would otherwise sit on the SMs for
+    // the whole scan, whose one warp a scheduler is slowed by every other resident warp.
+    fwb::pdl_wait();
     constexpr int COLS = 128 / LPC, STRIDE = DPL + 4, STAGES = 4;     // (+4: lanes' float4 reads hit apart banks)
-    __shared__ __align__(16) float kq[STAGES][2][LPC * STRIDE];
+    constexpr int KQ = 2 * LPC * STRIDE;                              // floats of one stage's k and q
+    __shared__ __align__(16) float kq[STAGES][KQ];
     __shared__ __align__(16) float vs[STAGES][COLS];
-    __shared__ float bg[STAGES][2];
+    __shared__ float scalars[STAGES][4];                              // beta, g, q.k
     const int seg = blockIdx.z, h = blockIdx.y;
     const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
     if (t1 <= t0) return;
@@ -155,81 +171,83 @@ delta_scan_kernel(const float* __restrict__ r, const float* __restrict__ p, floa
     }
     if (d < DPL * LPC || (int)(blockIdx.x + 1) * COLS > e) {
         // entries behind the head's last channel and columns behind the last are never copied: zeros
-        for (int i = threadIdx.x; i < STAGES * 2 * LPC * STRIDE; i += blockDim.x) (&kq[0][0][0])[i] = 0.0f;
+        for (int i = threadIdx.x; i < STAGES * KQ; i += blockDim.x) (&kq[0][0])[i] = 0.0f;
         for (int i = threadIdx.x; i < STAGES * COLS; i += blockDim.x) (&vs[0][0])[i] = 0.0f;
         __syncthreads();
     }
     const int q_at = kv_head * d, k_at = sh.cq() + kv_head * d, v_at = 2 * sh.cq() + h * e;
-    const int beta_at = sh.channels() + h, g_at = sh.channels() + sh.H + h;
+    // what this thread copies for every token (VEC): one 16-byte piece of k|q, the fourth warp's first
+    // lanes the values, three lanes the token's scalars
+    const int piece = threadIdx.x * 4;
+    const bool has_piece = piece < 2 * d;
+    const int piece_which = piece >= d ? 1 : 0, piece_dd = piece - piece_which * d;
+    const int piece_src = (piece_which ? q_at : k_at) + piece_dd;
+    const int piece_dst = piece_which * LPC * STRIDE + (piece_dd / DPL) * STRIDE + piece_dd % DPL;
+    const int c4 = (threadIdx.x - 96) * 4;
+    const bool has_v = threadIdx.x >= 96 && c4 < COLS && (int)blockIdx.x * COLS + c4 < e;
+    const int v_src = v_at + blockIdx.x * COLS + c4;
+    const int which_scalar = threadIdx.x - 120;                       // 0 beta, 1 g, 2 q.k
+    const int scalar_src = which_scalar == 0 ? sh.channels() + h
+                                             : (which_scalar == 1 ? sh.channels() + sh.H + h
+                                                                  : sh.channels() + 2 * sh.H + kv_head);
     auto fetch = [&](int t, int stage) {
         if (t < t1) {
             const float* row = r + (size_t)t * R;
             if (VEC) {
-                for (int i = threadIdx.x * 4; i < 2 * d; i += blockDim.x * 4) {
-                    const int which = i >= d ? 1 : 0, dd = i - which * d;
-                    copy_async_16(&kq[stage][which][(dd / DPL) * STRIDE + dd % DPL], row + (which ? q_at : k_at) + dd);
-                }
-                const int c4 = (threadIdx.x - 96) * 4;        // the fourth warp brings the values
-                if (threadIdx.x >= 96 && c4 < COLS && (int)blockIdx.x * COLS + c4 < e)
-                    copy_async_16(&vs[stage][c4], row + v_at + blockIdx.x * COLS + c4);
+                if (has_piece) copy_async_16(&kq[stage][piece_dst], row + piece_src);
+                if (has_v) copy_async_16(&vs[stage][c4], row + v_src);
             } else {
                 for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) {
                     const int which = i >= d ? 1 : 0, dd = i - which * d;
-                    copy_async_f32(&kq[stage][which][(dd / DPL) * STRIDE + dd % DPL], row + (which ? q_at : k_at) + dd);
+                    copy_async_f32(&kq[stage][which * LPC * STRIDE + (dd / DPL) * STRIDE + dd % DPL],
+                                   row + (which ? q_at : k_at) + dd);
                 }
                 if (threadIdx.x < COLS && blockIdx.x * COLS + threadIdx.x < e)
                     copy_async_f32(&vs[stage][threadIdx.x], row + v_at + blockIdx.x * COLS + threadIdx.x);
             }
-            if (threadIdx.x == 64) copy_async_f32(&bg[stage][0], row + beta_at);
-            if (threadIdx.x == 65) copy_async_f32(&bg[stage][1], row + g_at);
+            if (which_scalar >= 0 && which_scalar < 3) copy_async_f32(&scalars[stage][which_scalar], row + scalar_src);
         }
         copy_async_commit();
     };
     for (int j = 0; j < STAGES - 1; ++j) fetch(t0 + j, j);
-    for (int t = t0; t < t1; ++t) {
+    float* out_at = o + ((size_t)t0 * sh.H + h) * e + col;
+    const size_t out_step = (size_t)sh.H * e;
+    for (int t = t0; t < t1; ++t, out_at += out_step) {
         const int stage = (t - t0) % STAGES;
         copy_async_wait<STAGES - 2>();          // this token's copies have landed (mine; the barrier: everybody's)
         __syncthreads();                        // ... and everybody is done with the token before
         fetch(t + STAGES - 1, (t - t0 + STAGES - 1) % STAGES);
-        const float beta = bg[stage][0], g = bg[stage][1];
-        const float4* k4 = reinterpret_cast<const float4*>(&kq[stage][0][sub * STRIDE]);
-        const float4* q4 = reinterpret_cast<const float4*>(&kq[stage][1][sub * STRIDE]);
-        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int i = 0; i < DPL / 4; ++i) {
-            const float4 k = k4[i];
-            S[4 * i] *= g;
-            S[4 * i + 1] *= g;
-            S[4 * i + 2] *= g;
-            S[4 * i + 3] *= g;
-            part[0] = fmaf(S[4 * i], k.x, part[0]);
-            part[1] = fmaf(S[4 * i + 1], k.y, part[1]);
-            part[2] = fmaf(S[4 * i + 2], k.z, part[2]);
-            part[3] = fmaf(S[4 * i + 3], k.w, part[3]);
-        }
-        float dot = (part[0] + part[1]) + (part[2] + part[3]);
-#pragma unroll
-        for (int offset = 1; offset < LPC; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-        const float u = beta * (vs[stage][col_local] - dot);
-        part[0] = part[1] = part[2] = part[3] = 0.0f;
+        const float beta = scalars[stage][0], g = scalars[stage][1], qk = scalars[stage][2];
+        const float4* k4 = reinterpret_cast<const float4*>(&kq[stage][sub * STRIDE]);
+        const float4* q4 = reinterpret_cast<const float4*>(&kq[stage][LPC * STRIDE + sub * STRIDE]);
+        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f}, b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int i = 0; i < DPL / 4; ++i) {
             const float4 k = k4[i], q = q4[i];
-            S[4 * i] = fmaf(k.x, u, S[4 * i]);
-            S[4 * i + 1] = fmaf(k.y, u, S[4 * i + 1]);
-            S[4 * i + 2] = fmaf(k.z, u, S[4 * i + 2]);
-            S[4 * i + 3] = fmaf(k.w, u, S[4 * i + 3]);
-            part[0] = fmaf(S[4 * i], q.x, part[0]);
-            part[1] = fmaf(S[4 * i + 1], q.y, part[1]);
-            part[2] = fmaf(S[4 * i + 2], q.z, part[2]);
-            part[3] = fmaf(S[4 * i + 3], q.w, part[3]);
+            a[0] = fmaf(S[4 * i], k.x, a[0]), b[0] = fmaf(S[4 * i], q.x, b[0]);
+            a[1] = fmaf(S[4 * i + 1], k.y, a[1]), b[1] = fmaf(S[4 * i + 1], q.y, b[1]);
+            a[2] = fmaf(S[4 * i + 2], k.z, a[2]), b[2] = fmaf(S[4 * i + 2], q.z, b[2]);
+            a[3] = fmaf(S[4 * i + 3], k.w, a[3]), b[3] = fmaf(S[4 * i + 3], q.w, b[3]);
         }
-        float out = (part[0] + part[1]) + (part[2] + part[3]);
+        float sk = (a[0] + a[1]) + (a[2] + a[3]), sq = (b[0] + b[1]) + (b[2] + b[3]);
 #pragma unroll
-        for (int offset = 1; offset < LPC; offset <<= 1) out += __shfl_xor_sync(0xffffffffu, out, offset);
-        if (sub == 0 && valid) o[((size_t)t * sh.H + h) * e + col] = out;
+        for (int offset = 1; offset < LPC; offset <<= 1) {
+            sk += __shfl_xor_sync(0xffffffffu, sk, offset);
+            sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+        }
+        const float u = beta * (vs[stage][col_local] - g * sk);
+        if (sub == 0 && valid) *out_at = fmaf(g, sq, u * qk);
+#pragma unroll
+        for (int i = 0; i < DPL / 4; ++i) {
+            const float4 k = k4[i];
+            S[4 * i] = fmaf(g, S[4 * i], k.x * u);
+            S[4 * i + 1] = fmaf(g, S[4 * i + 1], k.y * u);
+            S[4 * i + 2] = fmaf(g, S[4 * i + 2], k.z * u);
+            S[4 * i + 3] = fmaf(g, S[4 * i + 3], k.w * u);
+        }
     }
     copy_async_wait<0>();
+    fwb::pdl_launch_dependents();
     if (VEC) {
 #pragma unroll
         for (int i = 0; i < DPL; i += 4) {
@@ -266,7 +284,7 @@ gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ ga
 
 // p: [T][2Gd + 2He + 2H] fp32 (q | k | v | gate | b | a).  taps: [2Gd + He][L] fp32.  a_log, dt_bias: [H].
 // state: [slots][slot_stride] fp32 with S at 0 and the convolution's inputs behind it.
-// r: [T][2Gd + He + 2H rounded up to a multiple of 4] fp32 scratch.  o: [T][H][e] fp32.
+// r: [T][2Gd + He + 2H + G rounded up to a multiple of 4] fp32 scratch.  o: [T][H][e] fp32.
 FWB_API int fwb_delta_rule(const float* p, const float* taps, const float* a_log, const float* dt_bias,
                            float* state, long long slot_stride, const int* seg_start, const int* seg_slot,
                            const int* tok_seg, float* r, float* o, int T, int n_segments, int H, int G, int d,

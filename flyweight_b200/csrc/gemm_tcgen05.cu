@@ -734,6 +734,11 @@ FWB_API int fwb_gemm_tcgen05_grouped(const void* X, const void* W, void* Y, cons
     if (epilogue != EPI_SWIGLU_BF16 && group_w_rows < N) return FWB_BAD_ARGUMENT;
     if (tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128) return FWB_BAD_ARGUMENT;
     if ((N + BM - 1) / BM > 65535) return FWB_TOO_LARGE;
+    // full token tiles and enough features: two 128-feature tiles a CTA, the rows read once for both
+    if (tile_rows == 128 && N >= 2 * BM) {
+        if (epilogue == EPI_F32) epilogue = EPI_F32_WIDE;
+        else if (epilogue == EPI_BF16) epilogue = EPI_BF16_WIDE;
+    }
     Params prm;
     prm.y = Y;
     prm.addend = nullptr;

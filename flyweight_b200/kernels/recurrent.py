@@ -42,7 +42,7 @@ def delta_rule(p: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias
     _i32("seg_start", batch.seg_start, S + 1)
     _i32("seg_slot", batch.seg_slot, S)
     _i32("tok_seg", batch.tok_seg, T)
-    r = torch.empty((T, -(-(channels + 2 * heads) // 4) * 4), dtype=torch.float32, device=p.device)
+    r = torch.empty((T, -(-(channels + 2 * heads + kv_heads) // 4) * 4), dtype=torch.float32, device=p.device)
     o = torch.empty((T, heads, vdim), dtype=torch.float32, device=p.device)
     lib.call("fwb_delta_rule", ptr(p), ptr(taps), ptr(a_log), ptr(dt_bias), ptr(state), c_longlong(stride),
              ptr(batch.seg_start), ptr(batch.seg_slot), ptr(batch.tok_seg), ptr(r), ptr(o), T, S, heads, kv_heads,

@@ -226,8 +226,13 @@ def forward(config, weights, tokens, dtype=torch.float64, keep_layers=False, rnd
         h = rnd(rms_norm(x, w[p + "norm1"], eps))
         mix = _layer_tensors(w, p + "mix.")
         if layer["type"] == "attention":
+            if m.get("kv_from") is not None:
+                # what a layer that reads another's keys leaves unsaid about them is the owner's
+                m = {**{key: config["layers"][int(m["kv_from"])]["mixer"][key] for key in ("kv_heads", "dim", "vdim", "rot")
+                        if key in config["layers"][int(m["kv_from"])]["mixer"]}, **m}
             H, G, d, e = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-            base, dims = float(m["rot"]["base"]), int(m["rot"]["dims"])
+            rot = m.get("rot") or {"base": 1.0, "dims": 0}            # no "rot": nothing turns
+            base, dims = float(rot["base"]), int(rot["dims"])
             if m.get("kv_from") is not None:
                 k, v = cached[int(m["kv_from"])]
             else:

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 NAMES = ("DA", "DB", "DC")
 
 
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ("DD", "DE"))
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_whole_prompts(name, dtype):
     runner = new_runner(name, dtype)
@@ -41,7 +41,7 @@ def test_prefill_against_token_by_token_decoding(name, dtype):
     assert_close(late, want, bound, "a prompt, then decoding")
 
 
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ("DD", "DE"))
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [(2,), (3, 2, 7, 1, 64, 2, 33), (63, 2, 64, 1, 1, 65), (128, 2), (47, 1, 1, 2)])
 def test_portions_of_any_size(name, dtype, sizes):
@@ -52,7 +52,7 @@ def test_portions_of_any_size(name, dtype, sizes):
                  f"portions {sizes}")
 
 
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ("DD", "DE"))
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_unequal_requests_in_one_batch_over_a_small_pool(name, dtype):
     """Up to four live requests, portions beside single tokens, requests left out of steps; the pool
@@ -65,7 +65,7 @@ def test_unequal_requests_in_one_batch_over_a_small_pool(name, dtype):
     for rid, ids in tokens.items():
         assert_close(got[rid], plain_logits(name, dtype, ids), oracle_bound(name, dtype, ids),
                      f"{name} {dtype} request {rid}")
-    assert runner.cache.groups[0].pool.n_used == 0
+    assert all(group.pool.n_used == 0 for group in runner.cache.groups)
     runner.check_health()
 
 

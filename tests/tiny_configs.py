@@ -173,7 +173,27 @@ DIFORAX_C = {
     ],
 }
 
-TINY.update({"DA": DIFORAX_A, "DB": DIFORAX_B, "DC": DIFORAX_C})
+# Models of one kind of mixer only: delta layers alone keep no pages at all (one query head per key head,
+# one layer without a feed-forward); attention layers alone, one of them with neither rotation nor chunks
+# (keys its configuration leaves out), the other reading its keys, with routers that leave `groups` out.
+DIFORAX_D = {
+    "architecture": "Diforax", "vocab": 97, "width": 48, "norm": {"eps": 1e-6},
+    "layers": [
+        {**_delta(3, 3, 12, 20, 3), "mlp": _dense(80)},
+        {**_delta(2, 1, 24, 16, 5), "mlp": None},
+    ],
+}
+DIFORAX_E = {
+    "architecture": "Diforax", "vocab": 160, "width": 64, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 32, "scale": 0.3},
+         "mlp": _experts(32, 4, 1, 2)},
+        {"type": "attention", "mixer": {"heads": 4, "scale": 0.2, "kv_from": 0, "mask": {"size": 33}},
+         "mlp": _experts(16, 2, 0, 2)},
+    ],
+}
+
+TINY.update({"DA": DIFORAX_A, "DB": DIFORAX_B, "DC": DIFORAX_C, "DD": DIFORAX_D, "DE": DIFORAX_E})
 
 
 def vocab_of(config: dict) -> int:
