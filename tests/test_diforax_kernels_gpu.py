@@ -460,6 +460,26 @@ ROUTERS = [  # outputs, groups, keep, top
 ]
 
 
+@pytest.mark.parametrize("W", [512, 520, 2112])
+@pytest.mark.parametrize("N,groups,keep,top", [(8, 4, 2, 3), (33, 1, 1, 5), (20, 5, 2, 6)])
+@pytest.mark.parametrize("dtype", BOTH)
+def test_router_over_wide_rows(W, N, groups, keep, top, dtype):
+    """Few tokens with rows of 512 entries and more take the kernel's other way through the products (K cut
+    over the warps): whole turns of all warps, a last turn that only some warps take part in, a last piece."""
+    from flyweight_b200.kernels import experts
+    g = torch.Generator().manual_seed(N + W)
+    T = 40
+    h = torch.randn(T, W, generator=g, dtype=F64)
+    h = bf16_round(h) if dtype == torch.bfloat16 else h.to(torch.float32).to(F64)
+    router = (torch.randn(N, W, generator=g, dtype=F64) / math.sqrt(W) * 2).to(torch.float32)
+    correction = (torch.randn(N, generator=g, dtype=F64) * 0.15).to(torch.float32)
+    ids, weights = experts.route(dev(h, dtype), dev(router), dev(correction), groups, keep, top)
+    want_ids, want_w = P.route(h, router.to(F64), correction.to(F64), groups, keep, top)
+    same = (ids.cpu().long() == want_ids).all(dim=1)
+    assert same.float().mean() > 0.95, f"{int((~same).sum())} of {T} tokens choose differently"
+    close(weights.cpu()[same], want_w[same], 1e-5, "weights")
+
+
 @pytest.mark.parametrize("N,groups,keep,top", ROUTERS)
 @pytest.mark.parametrize("dtype", BOTH)
 def test_router(N, groups, keep, top, dtype):
