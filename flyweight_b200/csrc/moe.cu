@@ -401,6 +401,44 @@ moe_combine_kernel(const float* __restrict__ y, const TH* __restrict__ h, const 
     }
 }
 
+// The weighted sum of a token's expert rows, the weighted RMS norm of that sum and the residual sum in
+// one pass: x[t] += w * y / sqrt(mean(y^2) + eps) with y as moe_combine_kernel makes it (same order of
+// additions), kept in shared memory between the two passes.
+template <typename TH>
+__global__ void __launch_bounds__(256)
+moe_combine_norm_add_kernel(const float* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ pair_row,
+                            const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ x,
+                            const float* __restrict__ norm_w, float eps, int W, int top, int E) {
+    fwb::pdl_entry();
+    constexpr int MAX_TOP = 64;
+    extern __shared__ float sum_row[];            // [W]
+    __shared__ int rows[MAX_TOP];
+    __shared__ float wts[MAX_TOP];
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    if (threadIdx.x < top) {
+        const int a = t * top + threadIdx.x;
+        const int row = pair_row[a];
+        rows[threadIdx.x] = row >= 0 ? row : (ids[a] >= E ? -1 : -2);
+        wts[threadIdx.x] = weights[a];
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = 0.0f;
+        const float own = to_f32<TH>(h[(size_t)t * W + i]);
+        for (int slot = 0; slot < top; ++slot) {
+            const int row = rows[slot];
+            const float v = row >= 0 ? y[(size_t)row * W + i] : (row == -1 ? own : 0.0f);
+            acc = fmaf(wts[slot], v, acc);
+        }
+        sum_row[i] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) x[(size_t)t * W + i] += (sum_row[i] * inv) * norm_w[i];
+}
+
 }  // namespace
 
 // h: [T][W] fp32 or bf16; router: [N][W] fp32; correction: [N] fp32; ids, weights: [T][top].
@@ -493,5 +531,28 @@ FWB_API int fwb_moe_combine(const float* y, const void* h, int h_bf16, const int
     else
         fwb::pdl(moe_combine_kernel<float>, T, 256, 0, stream)(y, (const float*)h, pair_row, ids, weights, out, W,
                                                                top, E);
+    return fwb_launch_status();
+}
+
+// The same sum, then x[t] += norm_w * sum / sqrt(mean(sum^2) + eps) in place (x: [T][W] fp32).
+FWB_API int fwb_moe_combine_norm_add(const float* y, const void* h, int h_bf16, const int* pair_row, const int* ids,
+                                     const float* weights, float* x, const float* norm_w, float eps, int T, int W,
+                                     int top, int E, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!y || !h || !pair_row || !ids || !weights || !x || !norm_w || W <= 0 || top <= 0) return FWB_BAD_ARGUMENT;
+    if (top > 64) return FWB_TOO_LARGE;
+    const size_t smem = (size_t)W * sizeof(float);
+    if (smem > 160 * 1024) return FWB_TOO_LARGE;
+    if (h_bf16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(moe_combine_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fwb::pdl(moe_combine_norm_add_kernel<__nv_bfloat16>, T, 256, smem, stream)(
+            y, (const __nv_bfloat16*)h, pair_row, ids, weights, x, norm_w, eps, W, top, E);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(moe_combine_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fwb::pdl(moe_combine_norm_add_kernel<float>, T, 256, smem, stream)(y, (const float*)h, pair_row, ids, weights, x,
+                                                                           norm_w, eps, W, top, E);
+    }
     return fwb_launch_status();
 }

@@ -36,10 +36,12 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, n_gro
 
 
 def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                    w_down: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+                    w_down: torch.Tensor, activation: str = "silu", add_normed_into=None):
     """``sum_slot weights * expert(h)`` as fp32 [T][W].  ``w_gate_up``: [E][2F][W] (gate rows, then up
     rows), ``w_down``: [E][W][F], both in the dtype of ``h``.  Router outputs from E on are identity
-    experts: they pass ``h`` itself on."""
+    experts: they pass ``h`` itself on.  ``add_normed_into`` = (x, norm weight, eps): the sum is not
+    returned but normed and added, ``x += weight * sum / sqrt(mean(sum^2) + eps)`` in fp32, by the kernel
+    that makes it (returns None)."""
     check_tensor("expert input", h)
     T, W = h.shape
     top = ids.shape[1]
@@ -82,6 +84,13 @@ def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
                  max_tiles, F, W, 1, act, stream())
         lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
                  max_tiles, W, F, 0, 0, stream())
+    if add_normed_into is not None:
+        x, norm_weight, eps = add_normed_into
+        check_tensor("residual", x, torch.float32, (T, W))
+        check_tensor("norm weight", norm_weight, torch.float32, (W,))
+        lib.call("fwb_moe_combine_norm_add", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(x),
+                 ptr(norm_weight), c_float(eps), T, W, top, E, stream())
+        return None
     out = torch.empty((T, W), dtype=torch.float32, device=dev)
     lib.call("fwb_moe_combine", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(out), T, W, top,
              E, stream())

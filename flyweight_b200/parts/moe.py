@@ -93,8 +93,14 @@ class RoutedExperts(FeedForward):
     def flops_per_token(self):
         return 2.0 * self.router.numel() + 2.0 * self.top * 3 * self.ffn_dim * self.hidden
 
-    def forward(self, ctx, h):
+    def forward(self, ctx, h, add_normed_into=None):
         ids, weights = expert_kernels.route(h, self.router, self.correction, self.groups, self.keep_groups, self.top)
         if h.dtype != self.w_gate_up.dtype:
             h = ops.cast(h, self.w_gate_up.dtype)
-        return expert_kernels.experts_forward(h, ids, weights, self.w_gate_up, self.w_down, self.activation)
+        return expert_kernels.experts_forward(h, ids, weights, self.w_gate_up, self.w_down, self.activation,
+                                              add_normed_into)
+
+    def forward_add_normed(self, ctx, h, x, norm_weight, eps):
+        """``x += norm_weight * unit(ff(h))`` with the weighted sum, the output norm and the residual sum in
+        one kernel (an arrangement with a norm on the sublayer's output asks for it)."""
+        self.forward(ctx, h, add_normed_into=(x, norm_weight, eps))

@@ -39,7 +39,10 @@ class SandwichResidual(Arrangement):
             return x, None
         w_next, eps_next = self.ffn_norm.plan_params()
         h = ops.rmsnorm_add_(x, y, w, eps, w_next, eps_next, act)
-        y = self.feed_forward.forward(ctx, h)
         w, eps = self.ffn_out_norm.plan_params()
-        ops.rmsnorm_add_(x, y, w, eps)
+        fused = getattr(self.feed_forward, "forward_add_normed", None)
+        if fused is not None:
+            fused(ctx, h, x, w, eps)           # the part's last kernel norms its output and adds it
+        else:
+            ops.rmsnorm_add_(x, self.feed_forward.forward(ctx, h), w, eps)
         return x, None

@@ -549,6 +549,15 @@ def test_routed_experts(dtype, hidden, ff, n_experts, identity, top, groups, kee
     plain_experts = [(w[f"e{j}.gate"], w[f"e{j}.up"], w[f"e{j}.down"]) for j in range(n_experts)]
     want = P.moe(h, w["router"], w["correction"], plain_experts, identity, groups, keep, top)
     close(got, want, 2e-5 if dtype == torch.float32 else 3 * 2.0 ** -7, "experts")
+    # the same with the output norm and the residual sum in the part's last kernel
+    from flyweight_b200.engine import StepContext
+    x = torch.randn(T, hidden, generator=g, dtype=torch.float32)
+    w_norm = 1 + 0.1 * torch.randn(hidden, generator=g, dtype=torch.float32)
+    xd = dev(x)
+    part.forward_add_normed(StepContext(Feeder(1).batch([(0, T)]), precision, DEV), dev(h, precision.act_dtype), xd,
+                            dev(w_norm), 1e-5)
+    close(xd, x.to(F64) + P.rms_norm(want, w_norm.to(F64), 1e-5), 2e-5 if dtype == torch.float32 else 3 * 2.0 ** -7,
+          "normed and added")
     # a token's result does not depend on what else is in the step
     if T > 5:
         alone = run_part(part, precision, [h[:3]], [[(0, 3)]], None, feed_forward=True)[0]
