@@ -424,16 +424,35 @@ moe_combine_norm_add_kernel(const float* __restrict__ y, const TH* __restrict__ 
     }
     __syncthreads();
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float acc = 0.0f;
-        const float own = to_f32<TH>(h[(size_t)t * W + i]);
-        for (int slot = 0; slot < top; ++slot) {
-            const int row = rows[slot];
-            const float v = row >= 0 ? y[(size_t)row * W + i] : (row == -1 ? own : 0.0f);
-            acc = fmaf(wts[slot], v, acc);
+    if ((W & 3) == 0) {
+        // rows of 16-byte pieces; every element is still its own sum over the slots, in slot order
+        const float4* y4 = reinterpret_cast<const float4*>(y);
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+            const TH* mine = h + (size_t)t * W + 4 * i;
+            const float4 own = make_float4(to_f32<TH>(mine[0]), to_f32<TH>(mine[1]), to_f32<TH>(mine[2]), to_f32<TH>(mine[3]));
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int slot = 0; slot < top; ++slot) {
+                const int row = rows[slot];
+                const float4 v = row >= 0 ? y4[(size_t)row * (W / 4) + i] : (row == -1 ? own : make_float4(0.f, 0.f, 0.f, 0.f));
+                const float wt = wts[slot];
+                acc.x = fmaf(wt, v.x, acc.x), acc.y = fmaf(wt, v.y, acc.y);
+                acc.z = fmaf(wt, v.z, acc.z), acc.w = fmaf(wt, v.w, acc.w);
+            }
+            reinterpret_cast<float4*>(sum_row)[i] = acc;
+            ss = fmaf(acc.x, acc.x, fmaf(acc.y, acc.y, fmaf(acc.z, acc.z, fmaf(acc.w, acc.w, ss))));
         }
-        sum_row[i] = acc;
-        ss = fmaf(acc, acc, ss);
+    } else {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            float acc = 0.0f;
+            const float own = to_f32<TH>(h[(size_t)t * W + i]);
+            for (int slot = 0; slot < top; ++slot) {
+                const int row = rows[slot];
+                const float v = row >= 0 ? y[(size_t)row * W + i] : (row == -1 ? own : 0.0f);
+                acc = fmaf(wts[slot], v, acc);
+            }
+            sum_row[i] = acc;
+            ss = fmaf(acc, acc, ss);
+        }
     }
     const float inv = rsqrtf(block_sum(ss, scratch) / (float)W + eps);
     for (int i = threadIdx.x; i < W; i += blockDim.x) x[(size_t)t * W + i] += (sum_row[i] * inv) * norm_w[i];
