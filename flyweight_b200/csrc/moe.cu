@@ -12,8 +12,10 @@
 //   gemm     one CTA per (row tile of one expert, tile of output features): rows gathered through the
 //            sorted list, fp32 FMA accumulation over k in order.  Form 1: act(x gate^T) * (x up^T) for
 //            the stacked matrix [gate rows | up rows]; form 0: the plain product in fp32.
+//   gather   the sorted rows' inputs side by side, for the grouped tensor-core product (bfloat16)
 //   combine  out[t] = sum over the token's pairs, in slot order, of weight * (expert row | h[t] itself
-//            for an identity expert).
+//            for an identity expert); alone, or followed in the same kernel by a weighted RMS norm of
+//            the sum and the residual sum, x[t] += w * unit(out[t]).
 // A pair's row is a sum over k in a fixed order whatever else is in the step, and a token's pairs are
 // added in slot order, so a token's result does not depend on the batch.  Grids are sized for the
 // worst case from the step's static sizes (every kernel reads the counts on the device), so a step

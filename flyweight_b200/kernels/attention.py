@@ -173,7 +173,9 @@ def tensor_core_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: int)
 
 
 def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype, sink=None):
-    """Causal GQA of every token of the step over its request's pages.  A cache with one pool
+    """Causal GQA of every token of the step over its request's pages.  ``window`` is the kernels' one
+    mask parameter: > 0 a sliding window of that many positions, < 0 chunks of ``-window`` positions
+    counted from position 0 (a query sees its own chunk up to itself), 0 every earlier key.  A cache with one pool
     (``v_pool`` None) holds rows that serve as keys and as values.  ``sink``: fp32 [n_heads], a score
     per head that joins every softmax denominator (not scaled, no value)."""
     batch = ctx.batch
