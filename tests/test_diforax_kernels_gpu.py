@@ -274,7 +274,7 @@ def test_a_layer_that_reads_another_layers_keys_under_its_own_chunk(dtype):
 # ------------------------------------------------------------------ one key that stands out, at every edge
 def edge_cases():
     cases = []
-    for chunk in (50, 64, 100, 200):
+    for chunk in (50, 64, 100, 130):
         for n in (chunk * 2 + 1, chunk * 3, 257, 450):
             first = (n - 1) // chunk * chunk              # the first position the last query sees
             for far in {first, first + 1, n - 1, first - 1, first - 2, 0, 63, 64, (first // 64) * 64 - 1}:
@@ -292,7 +292,7 @@ def test_one_key_that_stands_out_at_a_chunks_and_a_pages_edges(dtype, chunk, n, 
     a portion, through every attention kernel."""
     from flyweight_b200.engine import StepContext
     from flyweight_b200.kernels import attention, ops
-    heads, kv, hd = 8, 2, 64
+    heads, kv, hd = 12, 3, 64
     g = torch.Generator().manual_seed(chunk + n + far)
     keys = torch.randn(n, kv, hd, generator=g, dtype=F64) * 0.3
     values = torch.randn(n, kv, hd, generator=g, dtype=F64)
