@@ -142,7 +142,7 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
     }
     __syncwarp();
     // the (n_groups - keep) weakest runs leave the race, weakest first; ties: the higher index leaves
-    for (int round = 0; round < n_groups - keep; ++round) {
+    for (int out = 0; out < n_groups - keep; ++out) {
         float v = INFINITY;
         int at = -1;
         for (int g = lane; g < n_groups; g += 32)
